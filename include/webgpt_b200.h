@@ -1,0 +1,196 @@
+/*
+ * webgpt_b200 — C ABI of the B200 (sm_100a) implementation of WebGPT's GPT-2 forward path.
+ *
+ * Every entry point names the piece of the reference (0hq/WebGPT) it stands in for, as
+ * file:line inside that project. The reference drives a WebGPU device from JavaScript; a
+ * Node N-API addon (or any FFI) binds these functions one to one.
+ *
+ * Conventions
+ *  - All functions return a status code (WGPT_OK or a negative WGPT_ERR_*); nothing throws or
+ *    aborts across this boundary. wgpt_last_error() returns the message of the calling
+ *    thread's most recent failure.
+ *  - Device memory is passed as plain device addresses (void* / float* obtained from
+ *    wgpt_buffer_create or from any other CUDA allocation of the same device). Host memory is
+ *    named *_host.
+ *  - All work of a device is ordered on that device's stream. Calls that return data to the
+ *    host wait for it; every other call only enqueues.
+ *  - Matrices are row-major f32. "W[K,N]" is the reference's matmul weight layout
+ *    (instructions.js:219-224: B is [K,N], N contiguous).
+ *  - A handle may be used from one host thread at a time. Different devices may be driven
+ *    from different threads concurrently.
+ *  - There is no CPU fallback: a shape a kernel does not support returns
+ *    WGPT_ERR_UNSUPPORTED or WGPT_ERR_SHAPE.
+ */
+#ifndef WEBGPT_B200_H
+#define WEBGPT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WGPT_ABI_VERSION 1
+
+enum {
+  WGPT_OK = 0,
+  WGPT_ERR_SHAPE = -1,       /* a dimension violates a precondition (the reference throws) */
+  WGPT_ERR_ALIGN = -2,       /* a device address is not 16-byte aligned */
+  WGPT_ERR_OOM = -3,         /* device or host allocation failed */
+  WGPT_ERR_CUDA = -4,        /* a CUDA call failed; the message carries the CUDA error */
+  WGPT_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up */
+  WGPT_ERR_STATE = -6,       /* call not valid in the handle's current state */
+  WGPT_ERR_UNSUPPORTED = -7, /* valid in the reference, not implemented by these kernels */
+  WGPT_ERR_ARG = -8          /* null pointer, bad enum value, id out of range */
+};
+
+/* Arithmetic used by matrix products with more than 8 rows (prefill, batched decode).
+ * Products with up to 8 rows always run in FP32 on the CUDA cores. */
+enum {
+  WGPT_PRECISION_FP32 = 0,   /* FP32 FMA on the CUDA cores */
+  WGPT_PRECISION_TF32X3 = 1, /* tensor cores, three TF32 products per FP32 product (error ~1e-6) */
+  WGPT_PRECISION_TF32 = 2    /* tensor cores, single TF32 product (error ~1e-3) */
+};
+
+typedef struct wgpt_device wgpt_device;
+typedef struct wgpt_model wgpt_model;
+typedef struct wgpt_session wgpt_session;
+
+int32_t wgpt_abi_version(void);
+const char *wgpt_last_error(void);
+
+/* ---- device: GPT.initialize requestAdapter/requestDevice + initializeOperations
+ *      (model.js:27-30, globals.js:13-15); destroyOperations (globals.js:25-27). */
+int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out);
+int32_t wgpt_device_destroy(wgpt_device *dev);
+int32_t wgpt_device_synchronize(wgpt_device *dev);
+int32_t wgpt_device_set_precision(wgpt_device *dev, int32_t mode);
+/* Number of kernels this library has launched on the device since creation. */
+int32_t wgpt_device_launch_count(wgpt_device *dev, uint64_t *count);
+
+/* ---- buffers: Block.initBuffer / GPT.initTensor (instructions.js:67-81, model.js:490-500),
+ *      queue copies (model.js:253-255), mapAsync read-back (model.js:261-263). */
+int32_t wgpt_buffer_create(wgpt_device *dev, uint64_t bytes, void **dptr);
+int32_t wgpt_buffer_destroy(wgpt_device *dev, void *dptr);
+int32_t wgpt_buffer_write(wgpt_device *dev, void *dst, uint64_t dst_offset, const void *src_host, uint64_t bytes);
+int32_t wgpt_buffer_read(wgpt_device *dev, const void *src, uint64_t src_offset, void *dst_host, uint64_t bytes);
+int32_t wgpt_buffer_copy(wgpt_device *dev, const void *src, uint64_t src_offset, void *dst, uint64_t dst_offset,
+                         uint64_t bytes);
+/* Page-locked host memory for inputs/outputs of the calls below (optional; any host memory works). */
+int32_t wgpt_host_alloc(uint64_t bytes, void **ptr_host);
+int32_t wgpt_host_free(void *ptr_host);
+
+/* ---- timing on the device's stream (the reference times run() with performance.now(),
+ *      model.js:72-79). elapsed waits for the second event. */
+int32_t wgpt_event_create(wgpt_device *dev, void **event);
+int32_t wgpt_event_record(wgpt_device *dev, void *event);
+int32_t wgpt_event_elapsed_ms(wgpt_device *dev, void *start, void *stop, float *ms);
+int32_t wgpt_event_destroy(wgpt_device *dev, void *event);
+
+/* ---- per-operator entry points: one per instruction class of instructions.js ---- */
+
+/* FastMatMulBlock.newInstance(rows, cols, shared, input, weights, bias) (instructions.js:157-177),
+ * kernel fastMatMul (:179-319): out[rows,cols] = in[rows,shared] . W[shared,cols] + bias[cols].
+ * bias may be NULL. Requires cols % 8 == 0 (:158) and shared % 4 == 0. */
+int32_t wgpt_matmul(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in, const float *W,
+                    const float *bias, float *out);
+
+/* ResidualBlock.newInstance(rows, cols, outputBuf, residualBuf) (instructions.js:336-356; kernel :358-384).
+ * cols % 4 == 0 (:337). out may alias a or b. */
+int32_t wgpt_residual(wgpt_device *dev, int32_t rows, int32_t cols, const float *a, const float *b, float *out);
+
+/* LayerNormBlock.newInstance(rows, cols, input, gamma, beta) (instructions.js:409-448; kernels :451-550).
+ * eps = 1e-5 inside the square root. cols % 4 == 0 (:410). */
+int32_t wgpt_layernorm(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, const float *gamma,
+                       const float *beta, float *out);
+
+/* SoftmaxBlock.newInstance(rows, cols, input) (instructions.js:567-588; kernel :593-666), row softmax. */
+int32_t wgpt_softmax(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, float *out);
+
+/* GeluBlock.newInstance(rows, cols, input) (instructions.js:683-703; kernel :705-748). cols % 4 == 0 (:684). */
+int32_t wgpt_gelu(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, float *out);
+
+/* EmbedBlock.newInstance(idx, seq_length, n_embd, ...) (instructions.js:790-827):
+ * out[t,:] = wte[idx[t],:] + wpe[t,:]. idx lives on the device (u32). Ids >= vocab_size give
+ * WGPT_ERR_ARG after the kernel has run (the offending row is left zero). */
+int32_t wgpt_embed(wgpt_device *dev, const uint32_t *idx, int32_t seq_length, int32_t n_embd, int32_t vocab_size,
+                   const float *wte, const float *wpe, float *out);
+
+/* DeEmbedBlock.newInstance(n_embd, vocab_size, ..., seq_length, ...) (instructions.js:844-888; kernel :890-952):
+ * logits[v] = x[seq_length-1,:] . wte[v,:]. wte is the untransposed [vocab, n_embd] table: the
+ * reference's transposed, padded chunks (model.js:346-364) exist only to fit WebGPU binding limits. */
+int32_t wgpt_deembed(wgpt_device *dev, int32_t n_embd, int32_t vocab_size, int32_t seq_length, const float *x,
+                     const float *wte, float *logits);
+
+/* AttentionBlock.newFusedInstance(seq_length, n_embd, scale, n_head, head_size, input, qW, qB, kW, kB, vW, vB,
+ * linearW, linearB) (instructions.js:985-1099; kernels :1101-1214): causal self-attention over one window,
+ * out[seq_length, n_embd]. Weights are [n_embd, n_embd] in the W[K,N] layout. head_size must be one of
+ * 4, 8, 16, 32, 64, 128 and n_head * head_size == n_embd. */
+int32_t wgpt_attention(wgpt_device *dev, int32_t seq_length, int32_t n_embd, float scale, int32_t n_head,
+                       int32_t head_size, const float *in, const float *qW, const float *qB, const float *kW,
+                       const float *kB, const float *vW, const float *vB, const float *linW, const float *linB,
+                       float *out);
+
+/* int8 weight-only dequant-GEMM, the prototype of other/int8-gemm.js:117-229:
+ * out[M,N] = A[M,K] . (f32(q[K,N]) * scale[N]); Bq holds q packed four per 32-bit word along N,
+ * byte j of word w in row k = column 4w+j (:36-42), unpacked with sign extension (:126-131).
+ * scale is per output column (the prototype's header asks for vector-wise scales, :4). N % 8 == 0, K % 4 == 0. */
+int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int32_t N, const float *A, const uint32_t *Bq,
+                         const float *scale, float *out);
+
+/* ---- model level: class GPT of model.js ---- */
+
+/* params_gpt.json fields (model.js:289-322). bias is informational (model.js:322). */
+typedef struct wgpt_params {
+  int32_t n_layer, n_head, n_embd, n_ctx, vocab_size, bias;
+} wgpt_params;
+
+/* GPT.loadParameters checks (model.js:294-297): n_embd % 4, n_embd % n_head, head_size % 4. */
+int32_t wgpt_model_create(wgpt_device *dev, const wgpt_params *params, wgpt_model **out);
+/* GPT.loadEmbeddings/loadLayer/fetchAndInitTensor (model.js:339-500): name is the state-dict key of the
+ * on-disk file "<name>_gpt.bin" (e.g. "transformer.h.0.attn.c_attn.weight"), data the raw f32 contents in
+ * the on-disk layout ([in,out] for matmul weights), count its number of floats. The device copy is
+ * re-laid-out for the kernels, as the reference re-lays-out at load (model.js:362,456-468). */
+int32_t wgpt_model_set_tensor(wgpt_model *model, const char *name, const float *data_host, uint64_t count);
+/* Verifies every tensor was supplied; after this the model is read-only. */
+int32_t wgpt_model_finalize(wgpt_model *model);
+/* GPT.unloadBuffers (model.js:502-505). */
+int32_t wgpt_model_destroy(wgpt_model *model);
+
+/* A session holds the KV cache and activations of n_seq independent sequences of equal length. */
+int32_t wgpt_session_create(wgpt_model *model, int32_t n_seq, wgpt_session **out);
+int32_t wgpt_session_destroy(wgpt_session *session);
+int32_t wgpt_session_reset(wgpt_session *session);
+int32_t wgpt_session_length(wgpt_session *session, int32_t *length);
+
+/* Appends n_tok tokens to every sequence (ids_host is [n_seq, n_tok]) and, if logits_host is not NULL,
+ * returns the vocab logits of each sequence's newest position ([n_seq, vocab_size]). */
+int32_t wgpt_session_forward(wgpt_session *session, const uint32_t *ids_host, int32_t n_tok, float *logits_host);
+
+/* GPT.run(idx) (model.js:104-268): forward pass over the whole window idx[0..n), returns the vocab logits
+ * of the last position. The session (n_seq == 1) is reset first; it then holds the window's KV cache. */
+int32_t wgpt_model_run(wgpt_session *session, const uint32_t *idx_host, int32_t n, float *logits_host);
+
+/* GPT.generate with top_k = 1 (model.js:53-102, globals.js:47-74): feeds prompts_host [n_seq, n_prompt],
+ * then produces n_new greedy tokens per sequence into new_ids_host [n_seq, n_new]; arg-max, lowest index on
+ * ties. While a sequence fits in n_ctx every step reuses the KV cache; once the window would slide
+ * (model.js:69) each step recomputes the slid window, as the reference does. */
+int32_t wgpt_generate_greedy(wgpt_session *session, const uint32_t *prompts_host, int32_t n_prompt, int32_t n_new,
+                             uint32_t *new_ids_host);
+
+/* The three stages of wgpt_generate_greedy as separate calls, for callers that keep prompts resident or want to
+ * overlap: set_prompts uploads [n_seq, n_prompt] ids; generate only enqueues the whole greedy loop (no copy and,
+ * while n_prompt + n_new <= n_ctx, no host synchronisation) and may be repeated to regenerate from the same
+ * prompts; get_new_ids waits and copies the [n_seq, n_new] result to the host. */
+int32_t wgpt_session_set_prompts(wgpt_session *session, const uint32_t *prompts_host, int32_t n_prompt);
+int32_t wgpt_session_generate(wgpt_session *session, int32_t n_new);
+int32_t wgpt_session_get_new_ids(wgpt_session *session, int32_t n_new, uint32_t *new_ids_host);
+
+/* GPT.externalBuffer tap (model.js:18,211-222): copies the residual stream before ln_f of the most recent
+ * forward ([rows, n_embd], rows = n_seq * tokens of that call) into dst (device memory). */
+int32_t wgpt_session_tap(wgpt_session *session, float *dst, uint64_t max_floats, uint64_t *floats_written);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

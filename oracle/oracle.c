@@ -33,7 +33,7 @@
  * after the loop (:304-314). B is [K,N]. bias may be NULL (the int8 prototype and the de-embed
  * have none). */
 ORC_API void orc_matmul(const float *A, const float *B, const float *bias, float *C, int M, int K, int N) {
-  const int NB = 256; /* column block: keeps the accumulator strip in L1 */
+  const int NB = M < 8 ? 64 : 256; /* column block: an accumulator strip in L1; narrower when few rows must feed all threads */
 #pragma omp parallel for collapse(2) schedule(static)
   for (int m = 0; m < M; m++) {
     for (int n0 = 0; n0 < N; n0 += NB) {

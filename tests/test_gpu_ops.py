@@ -1,0 +1,174 @@
+"""GPU parity of each operator entry point of the C ABI against the CPU oracle (run with -m gpu)."""
+import numpy as np
+import pytest
+
+from conftest import load_golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-5  # relative, FP32 paths (the reference's own bound is 1e-3 absolute, validation.js:216)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from webgpt_b200 import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+@pytest.fixture(scope="module")
+def ops(dev):
+    from webgpt_b200 import globals as G
+    G.initializeOperations(dev)
+    yield G
+    G.destroyOperations()
+
+
+def run(inst):
+    for p in inst["passes"]:
+        assert p["flag"] == "compute"
+        p["run"]()
+    return inst["resultBuffer"]
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 8, 8), (1, 768, 2304), (3, 12, 16), (4, 384, 384), (8, 3072, 768),
+                                   (15, 128, 384), (33, 384, 1536), (256, 768, 768), (1, 1600, 6400)])
+def test_matmul(dev, ops, oracle, M, K, N):
+    rng = np.random.default_rng(M * 1000 + N)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = (rng.standard_normal((K, N), dtype=np.float32) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    out = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(b)))
+    got = out.read(np.float32, M * N).reshape(M, N)
+    assert rel_err(got, oracle.matmul(A, B, b)) < TOL
+    # deterministic: the split-K sums are added in a fixed order
+    out2 = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(b)))
+    assert np.array_equal(out2.read(np.float32, M * N).reshape(M, N), got)
+
+
+def test_matmul_rejects_bad_shapes(dev, ops):
+    from webgpt_b200 import WgptError, _lib
+    with pytest.raises(ValueError, match="divisible by 16"):
+        ops.FastMatMulBlock.newInstance(4, 12, 8, None, None, None)
+    a = dev.tensor(np.zeros(64, np.float32))
+    with pytest.raises(WgptError) as e:
+        _lib.call("wgpt_matmul", dev.handle, 1, 12, 8, a.ptr, a.ptr, None, a.ptr)
+    assert e.value.code == _lib.ERR_SHAPE and "divisible by 16" in e.value.message
+    with pytest.raises(WgptError) as e:
+        _lib.call("wgpt_matmul", dev.handle, 1, 8, 8, a.ptr + 4, a.ptr, None, a.ptr)
+    assert e.value.code == _lib.ERR_ALIGN
+    with pytest.raises(WgptError) as e:
+        _lib.call("wgpt_gelu", dev.handle, 1, 6, a.ptr, a.ptr)
+    assert "divisible by 4" in e.value.message
+
+
+@pytest.mark.parametrize("M,N", [(1, 4), (3, 60), (15, 384), (1, 768), (2, 5000), (64, 1600)])
+def test_elementwise_ops(dev, ops, oracle, M, N):
+    rng = np.random.default_rng(M + N)
+    x = (3 * rng.standard_normal((M, N))).astype(np.float32)
+    y = rng.standard_normal((M, N), dtype=np.float32)
+    g = rng.standard_normal(N, dtype=np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    xb, yb = dev.tensor(x), dev.tensor(y)
+    got = run(ops.ResidualBlock.newInstance(M, N, xb, yb)).read(np.float32, M * N).reshape(M, N)
+    assert np.array_equal(got, oracle.residual(x, y))  # one f32 add: bit exact
+    got = run(ops.LayerNormBlock.newInstance(M, N, xb, dev.tensor(g), dev.tensor(b))).read(np.float32, M * N)
+    assert np.max(np.abs(got.reshape(M, N) - oracle.layernorm(x, g, b))) < 2e-5
+    got = run(ops.GeluBlock.newInstance(M, N, xb)).read(np.float32, M * N).reshape(M, N)
+    assert np.max(np.abs(got - oracle.gelu(x))) < 2e-6
+    got = run(ops.SoftmaxBlock.newInstance(M, N, xb)).read(np.float32, M * N).reshape(M, N)
+    assert np.max(np.abs(got - oracle.softmax(x))) < 1e-6
+
+
+def test_gelu_clamps_and_softmax_odd(dev, ops, oracle):
+    edge = np.array([[-11.0, -10.0, 10.0, 11.0, 0.0, -0.0, 50.0, -50.0]], np.float32)
+    got = run(ops.GeluBlock.newInstance(1, 8, dev.tensor(edge))).read(np.float32, 8)
+    assert np.array_equal(got[[0, 3, 6, 7]], np.array([0.0, 11.0, 50.0, 0.0], np.float32))
+    for cols in (1, 3, 15, 33, 257):
+        x = np.random.default_rng(cols).standard_normal((5, cols)).astype(np.float32)
+        got = run(ops.SoftmaxBlock.newInstance(5, cols, dev.tensor(x))).read(np.float32, 5 * cols).reshape(5, cols)
+        assert np.max(np.abs(got - oracle.softmax(x))) < 1e-6
+
+
+def test_embed_deembed(dev, ops, oracle):
+    rng = np.random.default_rng(5)
+    V, E, T = 211, 128, 33
+    wte = rng.standard_normal((V, E), dtype=np.float32)
+    wpe = rng.standard_normal((64, E), dtype=np.float32)
+    idx = rng.integers(0, V, T).astype(np.uint32)
+    wb, pb = dev.tensor(wte), dev.tensor(wpe)
+    emb = run(ops.EmbedBlock.newInstance(idx, T, E, V, [wb], pb, ops.ResidualBlock))
+    got = emb.read(np.float32, T * E).reshape(T, E)
+    assert np.array_equal(got, oracle.embed(idx, wte, wpe))
+    logits = run(ops.DeEmbedBlock.newInstance(E, V, V, T, V, emb, [wb])).read(np.float32, V)
+    assert rel_err(logits, oracle.deembed(got[-1], wte)) < TOL
+    from webgpt_b200 import WgptError
+    bad = idx.copy()
+    bad[3] = V
+    with pytest.raises(WgptError, match="out of range"):
+        run(ops.EmbedBlock.newInstance(bad, T, E, V, [wb], pb, ops.ResidualBlock))
+
+
+@pytest.mark.parametrize("T,E,H", [(1, 32, 2), (3, 64, 4), (15, 128, 4), (33, 384, 6), (100, 768, 12), (40, 256, 2)])
+def test_attention(dev, ops, oracle, T, E, H):
+    rng = np.random.default_rng(T + E)
+    hs = E // H
+    x = rng.standard_normal((T, E), dtype=np.float32)
+    W = [(rng.standard_normal((E, E), dtype=np.float32) / np.sqrt(E)).astype(np.float32) for _ in range(4)]
+    b = [0.1 * rng.standard_normal(E, dtype=np.float32) for _ in range(4)]
+    scale = 1 / np.sqrt(hs)
+    t = dev.tensor
+    inst = ops.AttentionBlock.newFusedInstance(T, E, scale, H, hs, t(x), t(W[0]), t(b[0]), t(W[1]), t(b[1]), t(W[2]),
+                                               t(b[2]), t(W[3]), t(b[3]), ops.FastMatMulBlock, ops.SoftmaxBlock)
+    got = run(inst).read(np.float32, T * E).reshape(T, E)
+    ref = oracle.attention(x, H, np.float32(scale), W[0], b[0], W[1], b[1], W[2], b[2], W[3], b[3])
+    assert rel_err(got, ref) < TOL
+
+
+def test_attention_known_answer(dev, ops):
+    """The head-indexed pattern of other/test.js:370-388, pushed through the whole attention operator:
+    identity-like projections make Q.K constant per head so the softmax is uniform over the visible keys, and
+    V = head index + 1 must come back unchanged for every row."""
+    T, E, H = 15, 128, 4
+    hs = E // H
+    g = load_golden("attention_kat.npz")
+    x = g["V"]  # rows of (head index + 1)
+    eye = np.eye(E, dtype=np.float32)
+    z = np.zeros(E, np.float32)
+    t = dev.tensor
+    inst = ops.AttentionBlock.newFusedInstance(T, E, 1 / np.sqrt(hs), H, hs, t(x), t(eye), t(z), t(eye), t(z), t(eye),
+                                               t(z), t(eye), t(z))
+    got = run(inst).read(np.float32, T * E).reshape(T, E)
+    assert np.max(np.abs(got - x)) < 1e-5
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 768, 3072), (1, 3072, 768), (16, 768, 3072), (16, 1600, 6400), (4, 64, 32),
+                                   (3, 96, 64), (256, 768, 3072), (40, 128, 72)])
+def test_int8_matmul(dev, oracle, M, K, N):
+    from webgpt_b200 import _lib, synth
+    A, q, packed, scales = synth.make_int8_case(M, K, N)
+    out = dev.buffer(M * N * 4)
+    _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, dev.tensor(A).ptr, dev.tensor(packed).ptr,
+              dev.tensor(scales).ptr, out.ptr)
+    got = out.read(np.float32, M * N).reshape(M, N)
+    assert rel_err(got, oracle.int8_matmul(A, packed, scales, N)) < TOL
+    assert np.max(np.abs(got - oracle.int8_matmul(A, packed, scales, N, literal=True))) < 0.1  # int8-gemm.js:321
+
+
+@pytest.mark.parametrize("K", [8, 64, 40])
+def test_int8_unpack_bit_exact(dev, K):
+    """One-hot activations and unit scales read the unpacked integers back out of the kernel exactly; every byte
+    value appears in every lane."""
+    from webgpt_b200 import _lib
+    N = 1024
+    vals = np.arange(K * N, dtype=np.int64)
+    q = ((vals * 37 + vals // N) % 256).astype(np.uint8).view(np.int8).reshape(K, N)
+    packed = np.ascontiguousarray(q).view(np.uint32).reshape(K, N // 4)
+    for M in (1, K if K <= 16 else 16, K):
+        A = np.eye(K, dtype=np.float32)[:M]
+        out = dev.buffer(M * N * 4)
+        _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, dev.tensor(A).ptr, dev.tensor(packed).ptr,
+                  dev.tensor(np.ones(N, np.float32)).ptr, out.ptr)
+        got = out.read(np.float32, M * N).reshape(M, N)
+        assert np.array_equal(got, q[:M].astype(np.float32))

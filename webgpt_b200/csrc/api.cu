@@ -1,0 +1,1063 @@
+// C ABI of webgpt_b200 (declared in include/webgpt_b200.h): device/buffer management, the per-operator entry
+// points mirroring the reference's instruction classes, and the model/session level that mirrors class GPT.
+#include "../../include/webgpt_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "int8.cuh"
+#include "matmul.cuh"
+
+using namespace wgpt;
+
+#define WGPT_EXPORT extern "C" __attribute__((visibility("default")))
+
+// ------------------------------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+
+static int32_t fail(int32_t code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CK(call)                                                                                   \
+  do {                                                                                             \
+    cudaError_t e__ = (call);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      return fail(e__ == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "%s: %s", #call, \
+                  cudaGetErrorString(e__));                                                        \
+  } while (0)
+
+#define TRY(call)                 \
+  do {                            \
+    int32_t rc__ = (call);        \
+    if (rc__ != WGPT_OK) return rc__; \
+  } while (0)
+
+#define REQUIRE(cond, code, ...) \
+  do {                           \
+    if (!(cond)) return fail((code), __VA_ARGS__); \
+  } while (0)
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------------------------------ device
+struct wgpt_device {
+  int ordinal;
+  cudaStream_t stream;
+  int precision;
+  uint64_t launches;
+  int sm_count;
+  size_t smem_optin;
+  void *scratch;  // library-owned workspace (split-K partial sums, temporaries of wgpt_attention)
+  size_t scratch_cap;
+  int *d_err;     // device-side error word (out-of-range token id)
+};
+
+#define LAUNCH(dev, kernel, grid, block, smem, ...)                       \
+  do {                                                                    \
+    kernel<<<(grid), (block), (smem), (dev)->stream>>>(__VA_ARGS__);      \
+    (dev)->launches++;                                                    \
+    CK(cudaGetLastError());                                               \
+  } while (0)
+
+static int32_t use(wgpt_device *dev) {
+  REQUIRE(dev != nullptr, WGPT_ERR_ARG, "device handle is null");
+  CK(cudaSetDevice(dev->ordinal));
+  return WGPT_OK;
+}
+
+// Grows the workspace. Work already enqueued may still be using the old block, so drain first.
+static int32_t scratch_reserve(wgpt_device *dev, size_t bytes) {
+  if (bytes <= dev->scratch_cap) return WGPT_OK;
+  CK(cudaStreamSynchronize(dev->stream));
+  if (dev->scratch) CK(cudaFree(dev->scratch));
+  dev->scratch = nullptr;
+  dev->scratch_cap = 0;
+  size_t cap = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  CK(cudaMalloc(&dev->scratch, cap));
+  dev->scratch_cap = cap;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_abi_version(void) { return WGPT_ABI_VERSION; }
+WGPT_EXPORT const char *wgpt_last_error(void) { return g_err; }
+
+WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
+  REQUIRE(out != nullptr, WGPT_ERR_ARG, "out is null");
+  *out = nullptr;
+  int count = 0;
+  CK(cudaGetDeviceCount(&count));
+  REQUIRE(ordinal >= 0 && ordinal < count, WGPT_ERR_ARG, "device ordinal %d out of range (%d devices)", ordinal, count);
+  CK(cudaSetDevice(ordinal));
+  cudaDeviceProp prop;
+  CK(cudaGetDeviceProperties(&prop, ordinal));
+  // These kernels are built for sm_100a only; there is no other code path.
+  REQUIRE(prop.major == 10, WGPT_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only",
+          ordinal, prop.major, prop.minor);
+  wgpt_device *dev = new wgpt_device();
+  dev->ordinal = ordinal;
+  dev->precision = WGPT_PRECISION_FP32;
+  dev->launches = 0;
+  dev->sm_count = prop.multiProcessorCount;
+  dev->smem_optin = prop.sharedMemPerBlockOptin;
+  dev->scratch = nullptr;
+  dev->scratch_cap = 0;
+  dev->d_err = nullptr;
+  cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&dev->d_err, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream);
+  if (e != cudaSuccess) {
+    delete dev;
+    return fail(WGPT_ERR_CUDA, "device setup: %s", cudaGetErrorString(e));
+  }
+  *out = dev;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_device_destroy(wgpt_device *dev) {
+  TRY(use(dev));
+  cudaStreamSynchronize(dev->stream);
+  if (dev->scratch) cudaFree(dev->scratch);
+  if (dev->d_err) cudaFree(dev->d_err);
+  cudaStreamDestroy(dev->stream);
+  delete dev;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_device_synchronize(wgpt_device *dev) {
+  TRY(use(dev));
+  CK(cudaStreamSynchronize(dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_device_set_precision(wgpt_device *dev, int32_t mode) {
+  TRY(use(dev));
+  REQUIRE(mode >= WGPT_PRECISION_FP32 && mode <= WGPT_PRECISION_TF32, WGPT_ERR_ARG, "unknown precision mode %d", mode);
+  REQUIRE(mode == WGPT_PRECISION_FP32, WGPT_ERR_UNSUPPORTED, "tensor-core precision modes are not built yet");
+  dev->precision = mode;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_device_launch_count(wgpt_device *dev, uint64_t *count) {
+  REQUIRE(dev && count, WGPT_ERR_ARG, "null argument");
+  *count = dev->launches;
+  return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ buffers
+WGPT_EXPORT int32_t wgpt_buffer_create(wgpt_device *dev, uint64_t bytes, void **dptr) {
+  TRY(use(dev));
+  REQUIRE(dptr != nullptr, WGPT_ERR_ARG, "dptr is null");
+  *dptr = nullptr;
+  CK(cudaMalloc(dptr, bytes ? bytes : 16));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_buffer_destroy(wgpt_device *dev, void *dptr) {
+  TRY(use(dev));
+  if (!dptr) return WGPT_OK;
+  CK(cudaStreamSynchronize(dev->stream));
+  CK(cudaFree(dptr));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_buffer_write(wgpt_device *dev, void *dst, uint64_t off, const void *src_host, uint64_t bytes) {
+  TRY(use(dev));
+  REQUIRE(dst && (src_host || !bytes), WGPT_ERR_ARG, "null pointer");
+  if (!bytes) return WGPT_OK;
+  CK(cudaMemcpyAsync(static_cast<char *>(dst) + off, src_host, bytes, cudaMemcpyHostToDevice, dev->stream));
+  // The source may be pageable and reused by the caller right away.
+  CK(cudaStreamSynchronize(dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_buffer_read(wgpt_device *dev, const void *src, uint64_t off, void *dst_host, uint64_t bytes) {
+  TRY(use(dev));
+  REQUIRE(src && (dst_host || !bytes), WGPT_ERR_ARG, "null pointer");
+  if (bytes) CK(cudaMemcpyAsync(dst_host, static_cast<const char *>(src) + off, bytes, cudaMemcpyDeviceToHost, dev->stream));
+  CK(cudaStreamSynchronize(dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_buffer_copy(wgpt_device *dev, const void *src, uint64_t soff, void *dst, uint64_t doff,
+                                     uint64_t bytes) {
+  TRY(use(dev));
+  REQUIRE(src && dst, WGPT_ERR_ARG, "null pointer");
+  if (bytes)
+    CK(cudaMemcpyAsync(static_cast<char *>(dst) + doff, static_cast<const char *>(src) + soff, bytes,
+                       cudaMemcpyDeviceToDevice, dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_host_alloc(uint64_t bytes, void **p) {
+  REQUIRE(p != nullptr, WGPT_ERR_ARG, "ptr is null");
+  *p = nullptr;
+  CK(cudaMallocHost(p, bytes ? bytes : 16));
+  return WGPT_OK;
+}
+WGPT_EXPORT int32_t wgpt_host_free(void *p) {
+  if (p) CK(cudaFreeHost(p));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_event_create(wgpt_device *dev, void **event) {
+  TRY(use(dev));
+  REQUIRE(event != nullptr, WGPT_ERR_ARG, "event is null");
+  cudaEvent_t ev;
+  CK(cudaEventCreate(&ev));
+  *event = ev;
+  return WGPT_OK;
+}
+WGPT_EXPORT int32_t wgpt_event_record(wgpt_device *dev, void *event) {
+  TRY(use(dev));
+  CK(cudaEventRecord(static_cast<cudaEvent_t>(event), dev->stream));
+  return WGPT_OK;
+}
+WGPT_EXPORT int32_t wgpt_event_elapsed_ms(wgpt_device *dev, void *start, void *stop, float *ms) {
+  TRY(use(dev));
+  REQUIRE(ms != nullptr, WGPT_ERR_ARG, "ms is null");
+  CK(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+  CK(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+  return WGPT_OK;
+}
+WGPT_EXPORT int32_t wgpt_event_destroy(wgpt_device *dev, void *event) {
+  TRY(use(dev));
+  if (event) CK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ launch helpers
+static Epilogue plain_epi(float *out, int ld, const float *bias) {
+  Epilogue e;
+  memset(&e, 0, sizeof e);
+  e.out = out;
+  e.ld = ld;
+  e.bias = bias;
+  return e;
+}
+
+// Largest row count the staged-input GEMV handles for a given K (input rows live in shared memory).
+static bool gemv_nk_fits(const wgpt_device *dev, int M, int K) {
+  return M >= 1 && M <= 8 && (size_t)M * K * 4 + 8 * 4 * 8 * 4 <= dev->smem_optin - 1024;
+}
+
+template <int M, int WK, int CPW>
+static int32_t launch_gemv_nk_t(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
+                                const float *Wt, int K, int N, const Epilogue &epi) {
+  constexpr int WC = 8 / WK;
+  size_t smem = (size_t)M * K * 4 + (size_t)8 * CPW * M * 4;
+  auto kern = gemv_nk_kernel<M, WK, CPW>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int grid = (N + WC * CPW - 1) / (WC * CPW);
+  LAUNCH(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi);
+  return WGPT_OK;
+}
+
+template <int M>
+static int32_t launch_gemv_nk_m(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
+                                const float *Wt, int K, int N, const Epilogue &epi) {
+  // Enough warps to cover the machine several times over: split K across the warps of a CTA when N is small.
+  int wk = 1;
+  while (wk < 8 && (long long)N * wk < 3000 && K / (wk * 2) >= 256) wk *= 2;
+  if (N >= 16384) return launch_gemv_nk_t<M, 1, 4>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+  switch (wk) {
+    case 1: return launch_gemv_nk_t<M, 1, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 2: return launch_gemv_nk_t<M, 2, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 4: return launch_gemv_nk_t<M, 4, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    default: return launch_gemv_nk_t<M, 8, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+  }
+}
+
+static int32_t launch_gemv_nk(wgpt_device *dev, int M, const float *x, size_t ldx, const float *gamma,
+                              const float *beta, const float *Wt, int K, int N, const Epilogue &epi) {
+  switch (M) {
+    case 1: return launch_gemv_nk_m<1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 2: return launch_gemv_nk_m<2>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 3: return launch_gemv_nk_m<3>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 4: return launch_gemv_nk_m<4>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 5: return launch_gemv_nk_m<5>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 6: return launch_gemv_nk_m<6>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 7: return launch_gemv_nk_m<7>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 8: return launch_gemv_nk_m<8>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+  }
+  return fail(WGPT_ERR_SHAPE, "gemv rows %d out of range", M);
+}
+
+static int32_t launch_gemm_simt(wgpt_device *dev, bool b_nk, const float *A, size_t lda, const float *B, int M, int K,
+                                int N, const Epilogue &epi) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  if (b_nk)
+    LAUNCH(dev, gemm_simt_kernel<true>, grid, 256, 0, A, lda, B, M, K, N, epi);
+  else
+    LAUNCH(dev, gemm_simt_kernel<false>, grid, 256, 0, A, lda, B, M, K, N, epi);
+  return WGPT_OK;
+}
+
+static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in, const float *gamma, const float *beta,
+                                float *out, size_t ld_out, int rows, int N) {
+  LAUNCH(dev, layernorm_kernel, (rows + 3) / 4, 128, 0, in, ld_in, gamma, beta, out, ld_out, rows, N);
+  return WGPT_OK;
+}
+
+// K split for the [K,N]-layout GEMV: enough CTAs for about two per SM, at least 32 k rows per CTA.
+static int kn_ksplit(const wgpt_device *dev, int K, int col_groups) {
+  int want = (2 * dev->sm_count + col_groups - 1) / col_groups;
+  int maxs = K / 32 > 0 ? K / 32 : 1;
+  int s = want < maxs ? want : maxs;
+  return s < 1 ? 1 : s;
+}
+
+template <int M>
+static int32_t launch_gemv_kn_t(wgpt_device *dev, const float *x, const float *W, int K, int N, int ksplit,
+                                float *part) {
+  int klen_max = ((K / 4 + ksplit - 1) / ksplit + 1) * 4;
+  size_t smem = (size_t)M * klen_max * 4 + (size_t)8 * M * 32 * 16;
+  auto kern = gemv_kn_partial_kernel<M>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((N + 127) / 128, ksplit);
+  LAUNCH(dev, kern, grid, 256, smem, x, W, K, N, part);
+  return WGPT_OK;
+}
+
+// out = x[M,K] . W[K,N] (+ epilogue) for M <= 8, split-K with the partial sums in `part`
+// ([ksplit][M][N] floats, caller-provided).
+static int32_t gemv_kn_with_scratch(wgpt_device *dev, int M, const float *x, const float *W, int K, int N, int ksplit,
+                                    float *part, const Epilogue &epi) {
+  switch (M) {
+    case 1: TRY(launch_gemv_kn_t<1>(dev, x, W, K, N, ksplit, part)); break;
+    case 2: TRY(launch_gemv_kn_t<2>(dev, x, W, K, N, ksplit, part)); break;
+    case 3: TRY(launch_gemv_kn_t<3>(dev, x, W, K, N, ksplit, part)); break;
+    case 4: TRY(launch_gemv_kn_t<4>(dev, x, W, K, N, ksplit, part)); break;
+    case 5: TRY(launch_gemv_kn_t<5>(dev, x, W, K, N, ksplit, part)); break;
+    case 6: TRY(launch_gemv_kn_t<6>(dev, x, W, K, N, ksplit, part)); break;
+    case 7: TRY(launch_gemv_kn_t<7>(dev, x, W, K, N, ksplit, part)); break;
+    case 8: TRY(launch_gemv_kn_t<8>(dev, x, W, K, N, ksplit, part)); break;
+    default: return fail(WGPT_ERR_SHAPE, "gemv rows %d out of range", M);
+  }
+  int n4 = M * (N / 4);
+  LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, epi);
+  return WGPT_OK;
+}
+
+// The reference-layout matmul used by the per-operator API: W is [K,N].
+static int32_t matmul_kn(wgpt_device *dev, int M, int K, int N, const float *in, const float *W, const Epilogue &epi) {
+  if (M <= 8) {
+    int ksplit = kn_ksplit(dev, K, (N + 127) / 128);
+    TRY(scratch_reserve(dev, (size_t)ksplit * M * N * 4));
+    return gemv_kn_with_scratch(dev, M, in, W, K, N, ksplit, static_cast<float *>(dev->scratch), epi);
+  }
+  return launch_gemm_simt(dev, false, in, (size_t)K, W, M, K, N, epi);
+}
+
+template <int HS>
+static int32_t launch_attn_prefill_t(wgpt_device *dev, const float *q, int ldq, const float *kc, const float *vc,
+                                     int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_tok, int n_seq, int H,
+                                     const int *pos, float scale) {
+  size_t smem = attn_prefill_smem_bytes(HS);
+  auto kern = attn_prefill_kernel<HS>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((n_tok + 31) / 32, H, n_seq);
+  LAUNCH(dev, kern, grid, 128, smem, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok, pos, scale);
+  return WGPT_OK;
+}
+
+static int32_t launch_attn_prefill(wgpt_device *dev, int hs, const float *q, int ldq, const float *kc, const float *vc,
+                                   int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_tok, int n_seq, int H,
+                                   const int *pos, float scale) {
+#define CASE(HSV) \
+  case HSV: return launch_attn_prefill_t<HSV>(dev, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok, n_seq, H, pos, scale);
+  switch (hs) {
+    CASE(4) CASE(8) CASE(16) CASE(32) CASE(64) CASE(128)
+  }
+#undef CASE
+  return fail(WGPT_ERR_UNSUPPORTED, "head_size %d: supported sizes are 4, 8, 16, 32, 64, 128", hs);
+}
+
+static int32_t launch_attn_decode(wgpt_device *dev, int hs, const float *q, int ldq, const float *kc, const float *vc,
+                                  int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_seq, int H, int n_split,
+                                  const int *pos, float scale, float *part, unsigned int *counters) {
+  dim3 grid(H, n_seq, n_split);
+#define CASE(HSV)                                                                                             \
+  case HSV:                                                                                                   \
+    LAUNCH(dev, attn_decode_kernel<HSV>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
+           part, counters);                                                                                   \
+    return WGPT_OK;
+  switch (hs) {
+    CASE(4) CASE(8) CASE(16) CASE(32) CASE(64) CASE(128)
+  }
+#undef CASE
+  return fail(WGPT_ERR_UNSUPPORTED, "head_size %d: supported sizes are 4, 8, 16, 32, 64, 128", hs);
+}
+
+static int grid_for(size_t n, int block, int sm_count) {
+  size_t g = (n + block - 1) / block;
+  size_t cap = (size_t)sm_count * 16;
+  return (int)(g < cap ? (g ? g : 1) : cap);
+}
+
+// ------------------------------------------------------------------------------------------ per-operator API
+WGPT_EXPORT int32_t wgpt_matmul(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in,
+                                const float *W, const float *bias, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && W && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1 && shared >= 1, WGPT_ERR_SHAPE, "empty matmul %dx%dx%d", rows, cols, shared);
+  REQUIRE(cols % 8 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 16.");  // message of instructions.js:158
+  REQUIRE(shared % 4 == 0, WGPT_ERR_SHAPE, "shared dimension %d must be divisible by 4", shared);
+  REQUIRE(aligned16(in) && aligned16(W) && aligned16(out) && aligned16(bias), WGPT_ERR_ALIGN,
+          "buffers must be 16-byte aligned");
+  return matmul_kn(dev, rows, shared, cols, in, W, plain_epi(out, cols, bias));
+}
+
+WGPT_EXPORT int32_t wgpt_residual(wgpt_device *dev, int32_t rows, int32_t cols, const float *a, const float *b,
+                                  float *out) {
+  TRY(use(dev));
+  REQUIRE(a && b && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1, WGPT_ERR_SHAPE, "empty residual %dx%d", rows, cols);
+  REQUIRE(cols % 4 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 4.");  // instructions.js:337
+  REQUIRE(aligned16(a) && aligned16(b) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  size_t n4 = (size_t)rows * cols / 4;
+  LAUNCH(dev, residual_kernel, grid_for(n4, 256, dev->sm_count), 256, 0, reinterpret_cast<const float4 *>(a),
+         reinterpret_cast<const float4 *>(b), reinterpret_cast<float4 *>(out), n4);
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_gelu(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1, WGPT_ERR_SHAPE, "empty gelu %dx%d", rows, cols);
+  REQUIRE(cols % 4 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 4.");  // instructions.js:684
+  REQUIRE(aligned16(in) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  size_t n4 = (size_t)rows * cols / 4;
+  LAUNCH(dev, gelu_kernel, grid_for(n4, 256, dev->sm_count), 256, 0, reinterpret_cast<const float4 *>(in),
+         reinterpret_cast<float4 *>(out), n4);
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_layernorm(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, const float *gamma,
+                                   const float *beta, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && gamma && beta && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1, WGPT_ERR_SHAPE, "empty layernorm %dx%d", rows, cols);
+  REQUIRE(cols % 4 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 4.");  // instructions.js:410
+  REQUIRE(aligned16(in) && aligned16(gamma) && aligned16(beta) && aligned16(out), WGPT_ERR_ALIGN,
+          "buffers must be 16-byte aligned");
+  return launch_layernorm(dev, in, (size_t)cols, gamma, beta, out, (size_t)cols, rows, cols);
+}
+
+WGPT_EXPORT int32_t wgpt_softmax(wgpt_device *dev, int32_t rows, int32_t cols, const float *in, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1, WGPT_ERR_SHAPE, "empty softmax %dx%d", rows, cols);
+  LAUNCH(dev, softmax_kernel, (rows + 3) / 4, 128, 0, in, out, rows, cols);
+  return WGPT_OK;
+}
+
+static int32_t check_err_word(wgpt_device *dev, const char *what) {
+  int h = 0;
+  CK(cudaMemcpyAsync(&h, dev->d_err, sizeof h, cudaMemcpyDeviceToHost, dev->stream));
+  CK(cudaStreamSynchronize(dev->stream));
+  if (h) {
+    CK(cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream));
+    return fail(WGPT_ERR_ARG, "%s: token id out of range", what);
+  }
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_embed(wgpt_device *dev, const uint32_t *idx, int32_t seq_length, int32_t n_embd,
+                               int32_t vocab_size, const float *wte, const float *wpe, float *out) {
+  TRY(use(dev));
+  REQUIRE(idx && wte && wpe && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(seq_length >= 1 && vocab_size >= 1, WGPT_ERR_SHAPE, "empty embed");
+  REQUIRE(n_embd >= 4 && n_embd % 4 == 0, WGPT_ERR_SHAPE, "n_embd must be divisible by 4.");
+  REQUIRE(aligned16(wte) && aligned16(wpe) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  LAUNCH(dev, embed_kernel, seq_length, 128, 0, idx, wte, wpe, out, seq_length, seq_length, n_embd, vocab_size,
+         (const int *)nullptr, dev->d_err);
+  return check_err_word(dev, "wgpt_embed");
+}
+
+WGPT_EXPORT int32_t wgpt_deembed(wgpt_device *dev, int32_t n_embd, int32_t vocab_size, int32_t seq_length,
+                                 const float *x, const float *wte, float *logits) {
+  TRY(use(dev));
+  REQUIRE(x && wte && logits, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(seq_length >= 1 && vocab_size >= 1, WGPT_ERR_SHAPE, "empty deembed");
+  REQUIRE(n_embd >= 4 && n_embd % 4 == 0, WGPT_ERR_SHAPE, "n_embd must be divisible by 4.");
+  REQUIRE(aligned16(x) && aligned16(wte), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  REQUIRE(gemv_nk_fits(dev, 1, n_embd), WGPT_ERR_UNSUPPORTED, "n_embd %d too large", n_embd);
+  const float *x_last = x + (size_t)(seq_length - 1) * n_embd;  // slice copy of instructions.js:849-856
+  return launch_gemv_nk(dev, 1, x_last, (size_t)n_embd, nullptr, nullptr, wte, n_embd, vocab_size,
+                        plain_epi(logits, vocab_size, nullptr));
+}
+
+WGPT_EXPORT int32_t wgpt_attention(wgpt_device *dev, int32_t T, int32_t E, float scale, int32_t H, int32_t hs,
+                                   const float *in, const float *qW, const float *qB, const float *kW, const float *kB,
+                                   const float *vW, const float *vB, const float *linW, const float *linB, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && qW && kW && vW && linW && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(T >= 1 && E >= 8 && H >= 1, WGPT_ERR_SHAPE, "empty attention");
+  REQUIRE(E % 8 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 16.");
+  REQUIRE(H * hs == E, WGPT_ERR_SHAPE, "n_head * head_size (%d * %d) != n_embd (%d)", H, hs, E);
+  REQUIRE(aligned16(in) && aligned16(qW) && aligned16(kW) && aligned16(vW) && aligned16(linW) && aligned16(out) &&
+              aligned16(qB) && aligned16(kB) && aligned16(vB) && aligned16(linB),
+          WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  // workspace: q, k, v, o [T,E] + split-K partials
+  size_t te = (size_t)T * E;
+  int ksplit = T <= 8 ? kn_ksplit(dev, E, (E + 127) / 128) : 0;
+  size_t part_floats = (size_t)ksplit * T * E;
+  TRY(scratch_reserve(dev, (4 * te + part_floats) * 4));
+  float *q = static_cast<float *>(dev->scratch), *k = q + te, *v = k + te, *o = v + te, *part = o + te;
+  auto mm = [&](const float *a, const float *W, const float *b, float *dst) -> int32_t {
+    Epilogue e = plain_epi(dst, E, b);
+    if (T <= 8) return gemv_kn_with_scratch(dev, T, a, W, E, E, ksplit, part, e);
+    return launch_gemm_simt(dev, false, a, (size_t)E, W, T, E, E, e);
+  };
+  TRY(mm(in, qW, qB, q));
+  TRY(mm(in, kW, kB, k));
+  TRY(mm(in, vW, vB, v));
+  TRY(launch_attn_prefill(dev, hs, q, E, k, v, E, 0, o, E, T, 1, H, nullptr, scale));
+  return mm(o, linW, linB, out);
+}
+
+template <int M, int VEC>
+static int32_t launch_int8_gemv_t(wgpt_device *dev, const float *x, const uint32_t *Bq, int K, int N, int ksplit,
+                                  float *part) {
+  int klen_max = ((K / 4 + ksplit - 1) / ksplit + 1) * 4;
+  size_t smem = (size_t)M * klen_max * 4 + (size_t)8 * M * 32 * 4 * VEC * 4;
+  auto kern = int8_gemv_partial_kernel<M, VEC>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((N + 128 * VEC - 1) / (128 * VEC), ksplit);
+  LAUNCH(dev, kern, grid, 256, smem, x, Bq, K, N, part);
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int32_t N, const float *A,
+                                     const uint32_t *Bq, const float *scale, float *out) {
+  TRY(use(dev));
+  REQUIRE(A && Bq && scale && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(M >= 1 && K >= 4 && N >= 8, WGPT_ERR_SHAPE, "empty int8 matmul");
+  REQUIRE(N % 8 == 0 && K % 4 == 0, WGPT_ERR_SHAPE, "N must be divisible by 8 and K by 4");
+  REQUIRE(aligned16(A) && aligned16(Bq) && aligned16(scale) && aligned16(out), WGPT_ERR_ALIGN,
+          "buffers must be 16-byte aligned");
+  Epilogue e = plain_epi(out, N, nullptr);
+  e.colscale = scale;
+  if (M > 16) {
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    LAUNCH(dev, int8_gemm_simt_kernel, grid, 256, 0, A, Bq, M, K, N, e);
+    return WGPT_OK;
+  }
+  bool wide = (N % 16 == 0) && M <= 4;
+  int col_groups = wide ? (N + 511) / 512 : (N + 127) / 128;
+  int ksplit = kn_ksplit(dev, K, col_groups);
+  TRY(scratch_reserve(dev, (size_t)ksplit * M * N * 4));
+  float *part = static_cast<float *>(dev->scratch);
+#define CASE_W(MV) case MV: TRY((launch_int8_gemv_t<MV, 4>(dev, A, Bq, K, N, ksplit, part))); break;
+#define CASE_N(MV) case MV: TRY((launch_int8_gemv_t<MV, 1>(dev, A, Bq, K, N, ksplit, part))); break;
+  if (wide) {
+    switch (M) { CASE_W(1) CASE_W(2) CASE_W(3) CASE_W(4) }
+  } else {
+    switch (M) {
+      CASE_N(1) CASE_N(2) CASE_N(3) CASE_N(4) CASE_N(5) CASE_N(6) CASE_N(7) CASE_N(8)
+      CASE_N(9) CASE_N(10) CASE_N(11) CASE_N(12) CASE_N(13) CASE_N(14) CASE_N(15) CASE_N(16)
+    }
+  }
+#undef CASE_W
+#undef CASE_N
+  int n4 = M * (N / 4);
+  LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, e);
+  return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ model
+struct LayerWeights {
+  float *ln1_g, *ln1_b, *wqkv_t, *bqkv, *wo_t, *bo, *ln2_g, *ln2_b, *wfc_t, *bfc, *wpr_t, *bpr;
+};
+
+struct wgpt_model {
+  wgpt_device *dev;
+  wgpt_params p;
+  int hs;
+  float scale;
+  float *wte, *wpe, *lnf_g, *lnf_b;
+  std::vector<LayerWeights> layers;
+  std::vector<char> have;  // per tensor slot
+  bool finalized;
+  std::vector<void *> allocs;
+};
+
+static int32_t model_alloc(wgpt_model *m, float **p, size_t floats) {
+  CK(cudaMalloc(reinterpret_cast<void **>(p), floats * 4));
+  m->allocs.push_back(*p);
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_model_create(wgpt_device *dev, const wgpt_params *params, wgpt_model **out) {
+  TRY(use(dev));
+  REQUIRE(params && out, WGPT_ERR_ARG, "null argument");
+  *out = nullptr;
+  const wgpt_params &p = *params;
+  REQUIRE(p.n_layer >= 1 && p.n_head >= 1 && p.n_embd >= 1 && p.n_ctx >= 1 && p.vocab_size >= 1, WGPT_ERR_SHAPE,
+          "Model load failed: parameters must be positive.");
+  // messages of model.js:294-297
+  REQUIRE(p.n_embd % 4 == 0, WGPT_ERR_SHAPE, "Model load failed: n_embd must be divisible by 4.");
+  REQUIRE(p.n_embd % p.n_head == 0, WGPT_ERR_SHAPE, "Model load failed: n_embd must be divisible by n_head.");
+  REQUIRE((p.n_embd / p.n_head) % 4 == 0, WGPT_ERR_SHAPE, "Model load failed: n_embd / n_head must be divisible by 4.");
+  int hs = p.n_embd / p.n_head;
+  REQUIRE(hs == 4 || hs == 8 || hs == 16 || hs == 32 || hs == 64 || hs == 128, WGPT_ERR_UNSUPPORTED,
+          "head_size %d: supported sizes are 4, 8, 16, 32, 64, 128", hs);
+  wgpt_model *m = new wgpt_model();
+  m->dev = dev;
+  m->p = p;
+  m->hs = hs;
+  m->scale = (float)(1.0 / std::sqrt((double)hs));  // model.js:321, stored as f32 at instructions.js:1038
+  m->finalized = false;
+  m->layers.resize(p.n_layer);
+  m->have.assign(4 + 12 * (size_t)p.n_layer, 0);
+  size_t E = p.n_embd, F = 4 * E;
+  int32_t rc = WGPT_OK;
+  auto A = [&](float **ptr, size_t n) { if (rc == WGPT_OK) rc = model_alloc(m, ptr, n); };
+  A(&m->wte, (size_t)p.vocab_size * E);
+  A(&m->wpe, (size_t)p.n_ctx * E);
+  A(&m->lnf_g, E);
+  A(&m->lnf_b, E);
+  for (auto &L : m->layers) {
+    A(&L.ln1_g, E); A(&L.ln1_b, E); A(&L.wqkv_t, 3 * E * E); A(&L.bqkv, 3 * E); A(&L.wo_t, E * E); A(&L.bo, E);
+    A(&L.ln2_g, E); A(&L.ln2_b, E); A(&L.wfc_t, F * E); A(&L.bfc, F); A(&L.wpr_t, E * F); A(&L.bpr, E);
+  }
+  if (rc != WGPT_OK) {
+    for (void *q : m->allocs) cudaFree(q);
+    delete m;
+    return rc;
+  }
+  *out = m;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_model_destroy(wgpt_model *m) {
+  REQUIRE(m != nullptr, WGPT_ERR_ARG, "model handle is null");
+  TRY(use(m->dev));
+  cudaStreamSynchronize(m->dev->stream);
+  for (void *q : m->allocs) cudaFree(q);
+  delete m;
+  return WGPT_OK;
+}
+
+// Uploads a tensor; matmul weights arrive as [in,out] = [K,N] and are stored transposed as [N,K] so that
+// each output column's weights are contiguous (the reference also re-lays-out at load: model.js:362,456-468).
+static int32_t upload(wgpt_model *m, float *dst, const float *src_host, size_t rows, size_t cols, bool transpose) {
+  wgpt_device *dev = m->dev;
+  size_t n = rows * cols;
+  if (!transpose) {
+    CK(cudaMemcpyAsync(dst, src_host, n * 4, cudaMemcpyHostToDevice, dev->stream));
+    CK(cudaStreamSynchronize(dev->stream));
+    return WGPT_OK;
+  }
+  TRY(scratch_reserve(dev, n * 4));
+  CK(cudaMemcpyAsync(dev->scratch, src_host, n * 4, cudaMemcpyHostToDevice, dev->stream));
+  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+  LAUNCH(dev, transpose_kernel, grid, dim3(32, 8), 0, static_cast<const float *>(dev->scratch), dst, (int)rows,
+         (int)cols);
+  CK(cudaStreamSynchronize(dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_model_set_tensor(wgpt_model *m, const char *name, const float *data, uint64_t count) {
+  REQUIRE(m && name && data, WGPT_ERR_ARG, "null argument");
+  TRY(use(m->dev));
+  REQUIRE(!m->finalized, WGPT_ERR_STATE, "Model already loaded");
+  size_t E = m->p.n_embd, F = 4 * E, V = m->p.vocab_size, C = m->p.n_ctx;
+  std::string s(name);
+  float *dst = nullptr;
+  size_t rows = 1, cols = 0;
+  bool tr = false;
+  int slot = -1;
+  if (s == "transformer.wte.weight") { dst = m->wte; rows = V; cols = E; slot = 0; }
+  else if (s == "transformer.wpe.weight") { dst = m->wpe; rows = C; cols = E; slot = 1; }
+  else if (s == "transformer.ln_f.weight") { dst = m->lnf_g; cols = E; slot = 2; }
+  else if (s == "transformer.ln_f.bias") { dst = m->lnf_b; cols = E; slot = 3; }
+  else if (s.rfind("transformer.h.", 0) == 0) {
+    size_t dot = s.find('.', 14);
+    REQUIRE(dot != std::string::npos, WGPT_ERR_ARG, "unknown tensor name '%s'", name);
+    int l = atoi(s.substr(14, dot - 14).c_str());
+    REQUIRE(l >= 0 && l < m->p.n_layer, WGPT_ERR_ARG, "layer index out of range in '%s'", name);
+    std::string k = s.substr(dot + 1);
+    LayerWeights &L = m->layers[l];
+    int j = -1;
+    if (k == "ln_1.weight") { dst = L.ln1_g; cols = E; j = 0; }
+    else if (k == "ln_1.bias") { dst = L.ln1_b; cols = E; j = 1; }
+    else if (k == "attn.c_attn.weight") { dst = L.wqkv_t; rows = E; cols = 3 * E; tr = true; j = 2; }
+    else if (k == "attn.c_attn.bias") { dst = L.bqkv; cols = 3 * E; j = 3; }
+    else if (k == "attn.c_proj.weight") { dst = L.wo_t; rows = E; cols = E; tr = true; j = 4; }
+    else if (k == "attn.c_proj.bias") { dst = L.bo; cols = E; j = 5; }
+    else if (k == "ln_2.weight") { dst = L.ln2_g; cols = E; j = 6; }
+    else if (k == "ln_2.bias") { dst = L.ln2_b; cols = E; j = 7; }
+    else if (k == "mlp.c_fc.weight") { dst = L.wfc_t; rows = E; cols = F; tr = true; j = 8; }
+    else if (k == "mlp.c_fc.bias") { dst = L.bfc; cols = F; j = 9; }
+    else if (k == "mlp.c_proj.weight") { dst = L.wpr_t; rows = F; cols = E; tr = true; j = 10; }
+    else if (k == "mlp.c_proj.bias") { dst = L.bpr; cols = E; j = 11; }
+    REQUIRE(j >= 0, WGPT_ERR_ARG, "unknown tensor name '%s'", name);
+    slot = 4 + 12 * l + j;
+  }
+  REQUIRE(slot >= 0, WGPT_ERR_ARG, "unknown tensor name '%s'", name);
+  REQUIRE(count == rows * cols, WGPT_ERR_SHAPE, "tensor '%s' has %llu values, expected %llu", name,
+          (unsigned long long)count, (unsigned long long)(rows * cols));
+  TRY(upload(m, dst, data, rows, cols, tr));
+  m->have[slot] = 1;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
+  REQUIRE(m != nullptr, WGPT_ERR_ARG, "model handle is null");
+  for (size_t i = 0; i < m->have.size(); i++)
+    REQUIRE(m->have[i], WGPT_ERR_STATE, "tensor slot %zu was never set (4 + 12*layer + index)", i);
+  m->finalized = true;
+  return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ session
+struct wgpt_session {
+  wgpt_model *m = nullptr;
+  int n_seq = 0;
+  int len;       // tokens held per sequence (host mirror of *d_pos)
+  int cap_tok;   // tokens per forward the activation buffers are sized for
+  int out_cap;   // capacity (per sequence) of d_out_ids
+  int last_rows; // rows of the most recent forward (for the tap)
+  int n_split;
+  float *x, *h, *q, *o, *f, *logits;
+  float *kc, *vc;  // [n_layer][n_seq][n_ctx][E]
+  float *attn_part;
+  unsigned int *attn_cnt;
+  uint32_t *ids, *next_ids, *out_ids;
+  int *d_pos, *d_step;
+  std::vector<uint32_t> prompts;  // host copy, [n_seq][n_prompt]
+  int n_prompt, n_generated;
+  bool ids_dirty;  // s->ids no longer holds the prompt window
+};
+
+static void session_free_act(wgpt_session *s) {
+  cudaFree(s->x); cudaFree(s->h); cudaFree(s->q); cudaFree(s->o); cudaFree(s->f); cudaFree(s->ids);
+  s->x = s->h = s->q = s->o = s->f = nullptr;
+  s->ids = nullptr;
+}
+
+static int32_t session_reserve(wgpt_session *s, int n_tok) {
+  if (n_tok <= s->cap_tok) return WGPT_OK;
+  wgpt_device *dev = s->m->dev;
+  CK(cudaStreamSynchronize(dev->stream));
+  session_free_act(s);
+  s->cap_tok = 0;
+  size_t M = (size_t)s->n_seq * n_tok, E = s->m->p.n_embd;
+  CK(cudaMalloc(&s->x, M * E * 4)); CK(cudaMalloc(&s->h, M * E * 4)); CK(cudaMalloc(&s->q, M * E * 4));
+  CK(cudaMalloc(&s->o, M * E * 4)); CK(cudaMalloc(&s->f, M * 4 * E * 4)); CK(cudaMalloc(&s->ids, M * 4));
+  s->cap_tok = n_tok;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_session **out) {
+  REQUIRE(m && out, WGPT_ERR_ARG, "null argument");
+  *out = nullptr;
+  TRY(use(m->dev));
+  REQUIRE(m->finalized, WGPT_ERR_STATE, "Model not loaded yet");
+  REQUIRE(n_seq >= 1, WGPT_ERR_SHAPE, "n_seq must be at least 1");
+  wgpt_session *s = new wgpt_session();
+  s->m = m;
+  s->n_seq = n_seq;
+  const wgpt_params &p = m->p;
+  size_t kv = (size_t)p.n_layer * n_seq * p.n_ctx * p.n_embd;
+  int split = (2 * m->dev->sm_count) / (p.n_head * n_seq);
+  s->n_split = split < 1 ? 1 : (split > 16 ? 16 : split);
+  cudaError_t e = cudaMalloc(&s->kc, kv * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->vc, kv * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->logits, (size_t)n_seq * p.vocab_size * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 2) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, (size_t)n_seq * p.n_head * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->d_pos, 2 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemsetAsync(s->attn_cnt, 0, (size_t)n_seq * p.n_head * 4, m->dev->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), m->dev->stream);
+  if (e != cudaSuccess) {
+    cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
+    cudaFree(s->next_ids); cudaFree(s->d_pos);
+    delete s;
+    return fail(e == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "session allocation: %s",
+                cudaGetErrorString(e));
+  }
+  s->d_step = s->d_pos + 1;
+  *out = s;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
+  REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
+  TRY(use(s->m->dev));
+  cudaStreamSynchronize(s->m->dev->stream);
+  session_free_act(s);
+  cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
+  cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos);
+  delete s;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_reset(wgpt_session *s) {
+  REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
+  TRY(use(s->m->dev));
+  CK(cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), s->m->dev->stream));
+  s->len = 0;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_length(wgpt_session *s, int32_t *length) {
+  REQUIRE(s && length, WGPT_ERR_ARG, "null argument");
+  *length = s->len;
+  return WGPT_OK;
+}
+
+// One forward pass over n_tok new tokens per sequence whose ids are already in `ids` (device, [n_seq*n_tok]).
+// Leaves the logits of each sequence's newest position in s->logits. Does not advance the position.
+static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok) {
+  wgpt_model *m = s->m;
+  wgpt_device *dev = m->dev;
+  const wgpt_params &p = m->p;
+  const int E = p.n_embd, F = 4 * E, H = p.n_head, hs = m->hs, M = s->n_seq * n_tok;
+  const size_t kv_layer = (size_t)s->n_seq * p.n_ctx * E;
+
+  LAUNCH(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size, s->d_pos, dev->d_err);
+
+  auto mm = [&](const float *a, const float *gamma, const float *beta, const float *Wt, int K, int N,
+                const Epilogue &e) -> int32_t {
+    // a: [M,K] contiguous. Small M: weight-streaming GEMV with the LayerNorm fused in; otherwise a separate
+    // LayerNorm pass into s->h and a tiled GEMM.
+    if (gemv_nk_fits(dev, M, K)) return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
+    const float *src = a;
+    if (gamma) {
+      TRY(launch_layernorm(dev, a, (size_t)K, gamma, beta, s->h, (size_t)K, M, K));
+      src = s->h;
+    }
+    return launch_gemm_simt(dev, true, src, (size_t)K, Wt, M, K, N, e);
+  };
+
+  for (int l = 0; l < p.n_layer; l++) {
+    const LayerWeights &L = m->layers[l];
+    float *kc = s->kc + (size_t)l * kv_layer, *vc = s->vc + (size_t)l * kv_layer;
+    {  // LN1 + QKV projection; K and V rows go straight into the cache
+      Epilogue e = plain_epi(s->q, E, L.bqkv);
+      e.kc = kc; e.vc = vc; e.E = E; e.n_tok = n_tok; e.n_ctx = p.n_ctx; e.pos = s->d_pos;
+      TRY(mm(s->x, L.ln1_g, L.ln1_b, L.wqkv_t, E, 3 * E, e));
+    }
+    if (n_tok == 1)
+      TRY(launch_attn_decode(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, s->n_seq, H, s->n_split, s->d_pos,
+                             m->scale, s->attn_part, s->attn_cnt));
+    else
+      TRY(launch_attn_prefill(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, n_tok, s->n_seq, H, s->d_pos,
+                              m->scale));
+    {  // attention output projection + residual
+      Epilogue e = plain_epi(s->x, E, L.bo);
+      e.residual = s->x;
+      TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+    }
+    {  // LN2 + MLP up-projection + GELU
+      Epilogue e = plain_epi(s->f, F, L.bfc);
+      e.act = 1;
+      TRY(mm(s->x, L.ln2_g, L.ln2_b, L.wfc_t, E, F, e));
+    }
+    {  // MLP down-projection + residual
+      Epilogue e = plain_epi(s->x, E, L.bpr);
+      e.residual = s->x;
+      TRY(mm(s->f, nullptr, nullptr, L.wpr_t, F, E, e));
+    }
+  }
+  // ln_f + tied de-embedding on the newest row of each sequence only (the reference normalises all rows and
+  // then slices the last one, model.js:224-229 / instructions.js:849-856).
+  const float *x_last = s->x + (size_t)(n_tok - 1) * E;
+  size_t ld_last = (size_t)n_tok * E;
+  Epilogue e = plain_epi(s->logits, p.vocab_size, nullptr);
+  if (gemv_nk_fits(dev, s->n_seq, E)) {
+    TRY(launch_gemv_nk(dev, s->n_seq, x_last, ld_last, m->lnf_g, m->lnf_b, m->wte, E, p.vocab_size, e));
+  } else {
+    TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
+    TRY(launch_gemm_simt(dev, true, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
+  }
+  s->last_rows = M;
+  return WGPT_OK;
+}
+
+static int32_t advance(wgpt_session *s, int n_tok) {
+  LAUNCH(s->m->dev, advance_kernel, 1, 32, 0, s->d_pos, s->d_step, n_tok);
+  s->len += n_tok;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_forward(wgpt_session *s, const uint32_t *ids_host, int32_t n_tok, float *logits_host) {
+  REQUIRE(s && ids_host, WGPT_ERR_ARG, "null argument");
+  wgpt_device *dev = s->m->dev;
+  TRY(use(dev));
+  REQUIRE(n_tok >= 1, WGPT_ERR_SHAPE, "n_tok must be at least 1");
+  REQUIRE(s->len + n_tok <= s->m->p.n_ctx, WGPT_ERR_SHAPE, "sequence length %d + %d exceeds n_ctx %d", s->len, n_tok,
+          s->m->p.n_ctx);
+  TRY(session_reserve(s, n_tok));
+  size_t M = (size_t)s->n_seq * n_tok;
+  CK(cudaMemcpyAsync(s->ids, ids_host, M * 4, cudaMemcpyHostToDevice, dev->stream));
+  s->ids_dirty = true;
+  TRY(forward(s, s->ids, n_tok));
+  TRY(advance(s, n_tok));
+  if (logits_host)
+    CK(cudaMemcpyAsync(logits_host, s->logits, (size_t)s->n_seq * s->m->p.vocab_size * 4, cudaMemcpyDeviceToHost,
+                       dev->stream));
+  int32_t rc = check_err_word(dev, "wgpt_session_forward");  // also waits for the copies
+  if (rc != WGPT_OK) {
+    wgpt_session_reset(s);  // the cache now holds a row computed from a bad id
+    return rc;
+  }
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_model_run(wgpt_session *s, const uint32_t *idx_host, int32_t n, float *logits_host) {
+  REQUIRE(s && idx_host && logits_host, WGPT_ERR_ARG, "null argument");
+  REQUIRE(s->n_seq == 1, WGPT_ERR_STATE, "wgpt_model_run needs a session with one sequence");
+  REQUIRE(n >= 1 && n <= s->m->p.n_ctx, WGPT_ERR_SHAPE, "window length %d outside 1..n_ctx (%d)", n, s->m->p.n_ctx);
+  TRY(wgpt_session_reset(s));
+  return wgpt_session_forward(s, idx_host, n, logits_host);
+}
+
+static int32_t reserve_out_ids(wgpt_session *s, int n_new) {
+  if (n_new <= s->out_cap) return WGPT_OK;
+  CK(cudaStreamSynchronize(s->m->dev->stream));
+  cudaFree(s->out_ids);
+  s->out_ids = nullptr;
+  s->out_cap = 0;
+  CK(cudaMalloc(&s->out_ids, (size_t)s->n_seq * n_new * 4));
+  s->out_cap = n_new;
+  return WGPT_OK;
+}
+
+static int32_t pick(wgpt_session *s) {
+  LAUNCH(s->m->dev, argmax_kernel, s->n_seq, 1024, 0, s->logits, s->m->p.vocab_size, s->next_ids, s->out_ids,
+         s->out_cap, s->d_step);
+  return WGPT_OK;
+}
+
+// Host copy of the prompts (needed again only if the window slides) and their device copy.
+static int32_t set_prompts(wgpt_session *s, const uint32_t *prompts_host, int n_prompt) {
+  wgpt_device *dev = s->m->dev;
+  const int n_ctx = s->m->p.n_ctx, n_seq = s->n_seq;
+  // The newest n_ctx prompt tokens form the first window (history.slice(-n_ctx), model.js:69).
+  int first = n_prompt <= n_ctx ? n_prompt : n_ctx;
+  TRY(session_reserve(s, first));
+  TRY(wgpt_session_reset(s));
+  s->prompts.assign(prompts_host, prompts_host + (size_t)n_seq * n_prompt);
+  s->n_prompt = n_prompt;
+  for (int q = 0; q < n_seq; q++)
+    CK(cudaMemcpyAsync(s->ids + (size_t)q * first, prompts_host + (size_t)q * n_prompt + (n_prompt - first),
+                       (size_t)first * 4, cudaMemcpyHostToDevice, dev->stream));
+  // prompts_host may be pageable and is the caller's to reuse as soon as this returns
+  CK(cudaStreamSynchronize(dev->stream));
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_set_prompts(wgpt_session *s, const uint32_t *prompts_host, int32_t n_prompt) {
+  REQUIRE(s && prompts_host, WGPT_ERR_ARG, "null argument");
+  TRY(use(s->m->dev));
+  REQUIRE(n_prompt >= 1, WGPT_ERR_SHAPE, "n_prompt must be at least 1");
+  return set_prompts(s, prompts_host, n_prompt);
+}
+
+WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
+  REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
+  wgpt_device *dev = s->m->dev;
+  TRY(use(dev));
+  const int n_ctx = s->m->p.n_ctx, n_seq = s->n_seq, n_prompt = s->n_prompt;
+  REQUIRE(n_prompt >= 1, WGPT_ERR_STATE, "no prompts set");
+  REQUIRE(n_new >= 1, WGPT_ERR_SHAPE, "n_new must be at least 1");
+  TRY(reserve_out_ids(s, n_new));
+  int first = n_prompt <= n_ctx ? n_prompt : n_ctx;
+  // (Re)start from the prompt window held in s->ids by set_prompts; a repeated call regenerates from the prompt.
+  CK(cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), dev->stream));
+  s->len = 0;
+  if (s->ids_dirty) {
+    for (int q = 0; q < n_seq; q++)
+      CK(cudaMemcpyAsync(s->ids + (size_t)q * first, s->prompts.data() + (size_t)q * n_prompt + (n_prompt - first),
+                         (size_t)first * 4, cudaMemcpyHostToDevice, dev->stream));
+    CK(cudaStreamSynchronize(dev->stream));
+    s->ids_dirty = false;
+  }
+  TRY(forward(s, s->ids, first));
+  TRY(pick(s));
+  TRY(advance(s, first));
+  for (int i = 1; i < n_new; i++) {
+    if (s->len + 1 <= n_ctx) {
+      TRY(forward(s, s->next_ids, 1));
+      TRY(pick(s));
+      TRY(advance(s, 1));
+      continue;
+    }
+    // Window slides: every position index shifts, so the cache is void; recompute the newest n_ctx tokens
+    // from scratch as the reference does for every token (model.js:69-73). The ids produced so far come back
+    // to the host to build the window, one round trip per token like the reference's own loop.
+    std::vector<uint32_t> got((size_t)n_seq * s->out_cap);
+    CK(cudaMemcpyAsync(got.data(), s->out_ids, got.size() * 4, cudaMemcpyDeviceToHost, dev->stream));
+    CK(cudaStreamSynchronize(dev->stream));
+    TRY(session_reserve(s, n_ctx));
+    std::vector<uint32_t> window((size_t)n_seq * n_ctx);
+    for (int q = 0; q < n_seq; q++) {
+      std::vector<uint32_t> hist(s->prompts.begin() + (size_t)q * n_prompt, s->prompts.begin() + (size_t)(q + 1) * n_prompt);
+      hist.insert(hist.end(), got.begin() + (size_t)q * s->out_cap, got.begin() + (size_t)q * s->out_cap + i);
+      memcpy(window.data() + (size_t)q * n_ctx, hist.data() + (hist.size() - n_ctx), (size_t)n_ctx * 4);
+    }
+    CK(cudaMemsetAsync(s->d_pos, 0, sizeof(int), dev->stream));  // position only; the step counter keeps counting
+    s->len = 0;
+    CK(cudaMemcpyAsync(s->ids, window.data(), window.size() * 4, cudaMemcpyHostToDevice, dev->stream));
+    s->ids_dirty = true;
+    TRY(forward(s, s->ids, n_ctx));
+    TRY(pick(s));
+    TRY(advance(s, n_ctx));
+    CK(cudaStreamSynchronize(dev->stream));  // `window` is pageable host memory about to go out of scope
+  }
+  s->n_generated = n_new;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_session_get_new_ids(wgpt_session *s, int32_t n_new, uint32_t *new_ids_host) {
+  REQUIRE(s && new_ids_host, WGPT_ERR_ARG, "null argument");
+  wgpt_device *dev = s->m->dev;
+  TRY(use(dev));
+  REQUIRE(n_new >= 1 && n_new <= s->n_generated, WGPT_ERR_STATE, "only %d tokens have been generated", s->n_generated);
+  for (int q = 0; q < s->n_seq; q++)
+    CK(cudaMemcpyAsync(new_ids_host + (size_t)q * n_new, s->out_ids + (size_t)q * s->out_cap, (size_t)n_new * 4,
+                       cudaMemcpyDeviceToHost, dev->stream));
+  int32_t rc = check_err_word(dev, "generate");  // also waits for the copies
+  if (rc != WGPT_OK) wgpt_session_reset(s);
+  return rc;
+}
+
+WGPT_EXPORT int32_t wgpt_generate_greedy(wgpt_session *s, const uint32_t *prompts_host, int32_t n_prompt,
+                                         int32_t n_new, uint32_t *new_ids_host) {
+  REQUIRE(s && prompts_host && new_ids_host, WGPT_ERR_ARG, "null argument");
+  TRY(use(s->m->dev));
+  REQUIRE(n_prompt >= 1 && n_new >= 1, WGPT_ERR_SHAPE, "n_prompt and n_new must be at least 1");
+  TRY(set_prompts(s, prompts_host, n_prompt));
+  TRY(wgpt_session_generate(s, n_new));
+  return wgpt_session_get_new_ids(s, n_new, new_ids_host);
+}
+
+WGPT_EXPORT int32_t wgpt_session_tap(wgpt_session *s, float *dst, uint64_t max_floats, uint64_t *floats_written) {
+  REQUIRE(s && dst, WGPT_ERR_ARG, "null argument");
+  TRY(use(s->m->dev));
+  REQUIRE(s->last_rows > 0, WGPT_ERR_STATE, "no forward pass has run in this session");
+  uint64_t n = (uint64_t)s->last_rows * s->m->p.n_embd;
+  REQUIRE(n <= max_floats, WGPT_ERR_SHAPE, "tap needs room for %llu floats", (unsigned long long)n);
+  CK(cudaMemcpyAsync(dst, s->x, n * 4, cudaMemcpyDeviceToDevice, s->m->dev->stream));
+  if (floats_written) *floats_written = n;
+  return WGPT_OK;
+}

@@ -1,0 +1,222 @@
+// Causal attention over a KV cache, replacing the reference's formatQ + fusedWeights + softmax +
+// attentionValues chain (instructions.js:1101-1214, :593-666) without materialising the [H*T, T] score and
+// probability matrices. Masked scores are -1e9 in the reference (:1176) and exp(-1e9 - max) is exactly 0 in
+// f32, so skipping masked keys gives the same probabilities.
+//
+// Layout: Q rows [rows, ldq] with head h in columns [h*HS, (h+1)*HS); K and V rows for sequence s, position
+// j at base + (s*kv_seq_stride + j)*ldkv, same column convention (the reference's [T, E] K/V buffers).
+#pragma once
+#include "common.cuh"
+
+namespace wgpt {
+
+// ------------------------------------------------------------------------------------------------
+// Decode: one query row per sequence at position *pos (keys 0..*pos). grid = (H, n_seq, n_split);
+// each CTA (4 warps) handles a slice of the positions with an online softmax, writes an un-normalised
+// partial (max, sum, acc[HS]) to scratch, and the last CTA to finish for a (seq, head) merges the
+// slices in slice order. HBM-bound: reads 2*HS*4 bytes per position per head.
+// scratch: part[(seq*H + h)*n_split + s][HS + 2] floats, counters[seq*H + h] (zero before first use;
+// the merging CTA re-zeroes its counter).
+template <int HS>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc, const float *__restrict__ vc,
+                   int ldkv, size_t kv_seq_stride, float *__restrict__ out, int ldo, const int *__restrict__ pos,
+                   float scale, float *__restrict__ part, unsigned int *__restrict__ counters) {
+  constexpr int LPP = HS / 4;      // lanes per position (one float4 each)
+  constexpr int G = 32 / LPP;      // positions per warp iteration
+  const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, n_split = gridDim.z, H = gridDim.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane / LPP, lig = lane % LPP;
+  const int L = *pos + 1;
+  const int chunk = (L + n_split - 1) / n_split;
+  const int beg = split * chunk, end = min(L, beg + chunk);
+
+  const float4 q4 = *reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4);
+  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
+  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
+
+  float m = -INFINITY, l = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+  for (int j = beg + warp * G + g; j < end; j += 4 * G) {
+    float4 k4 = *reinterpret_cast<const float4 *>(kb + (size_t)j * ldkv);
+    float4 v4 = *reinterpret_cast<const float4 *>(vb + (size_t)j * ldkv);
+    float s = dot4(q4, k4);
+#pragma unroll
+    for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    s *= scale;
+    float mn = fmaxf(m, s);
+    float corr = expf(m - mn), p = expf(s - mn);  // m = -inf on the first key: corr = 0
+    l = l * corr + p;
+    acc.x = acc.x * corr + p * v4.x; acc.y = acc.y * corr + p * v4.y;
+    acc.z = acc.z * corr + p * v4.z; acc.w = acc.w * corr + p * v4.w;
+    m = mn;
+  }
+  // A loop with a lane-dependent trip count ends with the groups of a warp diverged; re-converge.
+  __syncwarp();
+  // merge the G groups of the warp
+#pragma unroll
+  for (int o = LPP; o < 32; o <<= 1) {
+    float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
+    float4 ao;
+    ao.x = __shfl_xor_sync(0xffffffffu, acc.x, o); ao.y = __shfl_xor_sync(0xffffffffu, acc.y, o);
+    ao.z = __shfl_xor_sync(0xffffffffu, acc.z, o); ao.w = __shfl_xor_sync(0xffffffffu, acc.w, o);
+    float mn = fmaxf(m, mo);
+    float c0 = (m == -INFINITY) ? 0.f : expf(m - mn), c1 = (mo == -INFINITY) ? 0.f : expf(mo - mn);
+    l = l * c0 + lo * c1;
+    acc.x = acc.x * c0 + ao.x * c1; acc.y = acc.y * c0 + ao.y * c1;
+    acc.z = acc.z * c0 + ao.z * c1; acc.w = acc.w * c0 + ao.w * c1;
+    m = mn;
+  }
+  __shared__ float sm_m[4], sm_l[4];
+  __shared__ __align__(16) float sm_acc[4][HS];
+  if (g == 0) {
+    *reinterpret_cast<float4 *>(&sm_acc[warp][lig * 4]) = acc;
+    if (lig == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+  }
+  __syncthreads();
+  float *my = part + ((size_t)(seq * H + h) * n_split + split) * (HS + 2);
+  if (tid < HS) {
+    float mm = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - mm);
+      ll += sm_l[w] * c;
+      a += sm_acc[w][tid] * c;
+    }
+    if (n_split == 1) {
+      out[(size_t)seq * ldo + h * HS + tid] = a / ll;
+      return;
+    }
+    my[2 + tid] = a;
+    if (tid == 0) { my[0] = mm; my[1] = ll; }
+  }
+  if (n_split == 1) return;
+  // ---- last CTA of this (seq, head) merges the slices ----
+  __shared__ unsigned int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int prev = atomicAdd(&counters[seq * H + h], 1u);
+    is_last = (prev == (unsigned int)n_split - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (tid < HS) {
+    const float *p0 = part + (size_t)(seq * H + h) * n_split * (HS + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < n_split; s++) mm = fmaxf(mm, __ldcg(p0 + (size_t)s * (HS + 2)));
+    float ll = 0.f, a = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      float ms = __ldcg(p0 + (size_t)s * (HS + 2));
+      float c = (ms == -INFINITY) ? 0.f : expf(ms - mm);
+      ll += __ldcg(p0 + (size_t)s * (HS + 2) + 1) * c;
+      a += __ldcg(p0 + (size_t)s * (HS + 2) + 2 + tid) * c;
+    }
+    out[(size_t)seq * ldo + h * HS + tid] = a / ll;
+  }
+  if (tid == 0) counters[seq * H + h] = 0u;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prefill: n_tok new query rows per sequence at positions *pos .. *pos+n_tok-1, keys 0..position.
+// grid = (ceil(n_tok/32), H, n_seq), 128 threads: a 32-query tile against 32-key tiles held in shared
+// memory, online softmax per query row. Thread (qi = tid/4, sub = tid%4) owns keys sub, sub+4, ... of the
+// tile for the scores and dims sub, sub+4, ... of the output.
+constexpr size_t attn_prefill_smem_bytes(int hs) { return (size_t)(96 * (hs + 1) + 32 * 33) * sizeof(float); }
+
+template <int HS>
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc, const float *__restrict__ vc,
+                    int ldkv, size_t kv_seq_stride, float *__restrict__ out, int ldo, int n_tok,
+                    const int *__restrict__ pos, float scale) {
+  constexpr int TQ = 32, TK = 32, LD = HS + 1, DPT = HS / 4;
+  extern __shared__ float attn_smem[];  // attn_prefill_smem_bytes(HS): above 48 KB for HS = 128
+  float (*Qs)[LD] = reinterpret_cast<float (*)[LD]>(attn_smem);
+  float (*Ks)[LD] = reinterpret_cast<float (*)[LD]>(attn_smem + TQ * LD);
+  float (*Vs)[LD] = reinterpret_cast<float (*)[LD]>(attn_smem + (TQ + TK) * LD);
+  float (*Ps)[TK + 1] = reinterpret_cast<float (*)[TK + 1]>(attn_smem + (TQ + 2 * TK) * LD);
+  const int h = blockIdx.y, seq = blockIdx.z, t0 = blockIdx.x * TQ;
+  const int tid = threadIdx.x, qi = tid >> 2, sub = tid & 3;
+  const int pos0 = pos ? *pos : 0;
+  const int nq = min(TQ, n_tok - t0);
+  const int my_t = t0 + min(qi, nq - 1);       // out-of-range query threads shadow the last valid row
+  const int my_pos = pos0 + my_t;
+  const int last_key = pos0 + t0 + nq - 1;     // newest key any query of this tile may see
+
+  for (int i = tid; i < TQ * (HS / 4); i += 128) {
+    int r = i / (HS / 4), c4 = (i % (HS / 4)) * 4;
+    int t = t0 + min(r, nq - 1);
+    float4 v = *reinterpret_cast<const float4 *>(q + ((size_t)seq * n_tok + t) * ldq + h * HS + c4);
+    Qs[r][c4] = v.x; Qs[r][c4 + 1] = v.y; Qs[r][c4 + 2] = v.z; Qs[r][c4 + 3] = v.w;
+  }
+  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+
+  float m = -INFINITY, l = 0.f, o[DPT];
+#pragma unroll
+  for (int d = 0; d < DPT; d++) o[d] = 0.f;
+
+  for (int j0 = 0; j0 <= last_key; j0 += TK) {
+    __syncthreads();
+    for (int i = tid; i < TK * (HS / 4); i += 128) {
+      int r = i / (HS / 4), c4 = (i % (HS / 4)) * 4;
+      int j = min(j0 + r, last_key);
+      float4 kv = *reinterpret_cast<const float4 *>(kb + (size_t)j * ldkv + c4);
+      float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)j * ldkv + c4);
+      Ks[r][c4] = kv.x; Ks[r][c4 + 1] = kv.y; Ks[r][c4 + 2] = kv.z; Ks[r][c4 + 3] = kv.w;
+      Vs[r][c4] = vv.x; Vs[r][c4 + 1] = vv.y; Vs[r][c4 + 2] = vv.z; Vs[r][c4 + 3] = vv.w;
+    }
+    __syncthreads();
+    float s[TK / 4];
+#pragma unroll
+    for (int kk = 0; kk < TK / 4; kk++) s[kk] = 0.f;
+    for (int d = 0; d < HS; d++) {
+      float qv = Qs[qi][d];
+#pragma unroll
+      for (int kk = 0; kk < TK / 4; kk++) s[kk] += qv * Ks[sub + 4 * kk][d];
+    }
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int kk = 0; kk < TK / 4; kk++) {
+      int j = j0 + sub + 4 * kk;
+      s[kk] = (j <= my_pos) ? s[kk] * scale : -INFINITY;
+      tmax = fmaxf(tmax, s[kk]);
+    }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    float mn = fmaxf(m, tmax);  // key j0 <= my_pos is visible in every processed tile? no: guard below
+    float corr = (m == -INFINITY) ? 0.f : expf(m - mn);
+    float psum = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < TK / 4; kk++) {
+      float p = (s[kk] == -INFINITY) ? 0.f : expf(s[kk] - mn);
+      Ps[qi][sub + 4 * kk] = p;
+      psum += p;
+    }
+    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+    if (mn != -INFINITY) {
+      l = l * corr + psum;
+      m = mn;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int d = 0; d < DPT; d++) o[d] *= corr;
+    for (int k = 0; k < TK; k++) {
+      float p = Ps[qi][k];
+#pragma unroll
+      for (int d = 0; d < DPT; d++) o[d] += p * Vs[k][sub + 4 * d];
+    }
+  }
+  if (qi < nq) {
+    float *op = out + ((size_t)seq * n_tok + t0 + qi) * ldo + h * HS;
+    float inv = 1.f / l;
+#pragma unroll
+    for (int d = 0; d < DPT; d++) op[sub + 4 * d] = o[d] * inv;
+  }
+}
+
+}  // namespace wgpt

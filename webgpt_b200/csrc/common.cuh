@@ -1,0 +1,104 @@
+// Shared device helpers for the sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wgpt {
+
+constexpr int kWarp = 32;
+
+// Where a matmul result goes and what is applied to it on the way out.
+// Fuses the reference's separate bias add (instructions.js:304-314), GELU pass (:705-748) and
+// residual pass (:358-384) into the producing kernel, and lets the QKV projection write K and V
+// rows straight into the KV cache.
+struct Epilogue {
+  const float *colscale;  // [N] or nullptr: multiplies the raw product (int8 per-column dequant scale)
+  const float *bias;      // [N] or nullptr
+  const float *residual;  // [M, ld] or nullptr; may alias out
+  float *out;             // [M, ld]
+  int ld;
+  int act;                // 1 = GELU
+  // KV scatter (kc != nullptr): columns [E,2E) go to kc, [2E,3E) to vc; row m = seq*n_tok + t
+  // lands in cache row seq*n_ctx + *pos + t.
+  float *kc, *vc;
+  int E, n_tok, n_ctx;
+  const int *pos;
+};
+
+__device__ __forceinline__ float gelu_f(float x) {
+  // instructions.js:711-727
+  float x3 = x * x * x;
+  float r = x * (0.5f * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x3))));
+  r = x < -10.0f ? 0.0f : r;
+  return x > 10.0f ? x : r;
+}
+
+// Address of element (m, n) of the epilogue's destination. n..n+3 stay in one section when E % 4 == 0.
+__device__ __forceinline__ float *epi_addr(const Epilogue &e, int m, int n) {
+  if (e.kc == nullptr || n < e.E) return e.out + (size_t)m * e.ld + n;
+  int sec = n >= 2 * e.E ? 2 : 1;
+  int c = n - sec * e.E;
+  int seq = m / e.n_tok, t = m - seq * e.n_tok;
+  size_t row = (size_t)seq * e.n_ctx + (size_t)(*e.pos) + t;
+  return (sec == 1 ? e.kc : e.vc) + row * e.E + c;
+}
+
+__device__ __forceinline__ float epi_apply(const Epilogue &e, float v, int m, int n) {
+  if (e.colscale) v *= e.colscale[n];
+  if (e.bias) v += e.bias[n];
+  if (e.act == 1) v = gelu_f(v);
+  if (e.residual) v += e.residual[(size_t)m * e.ld + n];
+  return v;
+}
+
+__device__ __forceinline__ void epi_store(const Epilogue &e, float v, int m, int n) {
+  *epi_addr(e, m, n) = epi_apply(e, v, m, n);
+}
+
+__device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, int n) {
+  if (e.colscale) {
+    float4 c = *reinterpret_cast<const float4 *>(e.colscale + n);
+    v.x *= c.x; v.y *= c.y; v.z *= c.z; v.w *= c.w;
+  }
+  if (e.bias) {
+    float4 b = *reinterpret_cast<const float4 *>(e.bias + n);
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  if (e.act == 1) { v.x = gelu_f(v.x); v.y = gelu_f(v.y); v.z = gelu_f(v.z); v.w = gelu_f(v.w); }
+  if (e.residual) {
+    float4 r = *reinterpret_cast<const float4 *>(e.residual + (size_t)m * e.ld + n);
+    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+  }
+  *reinterpret_cast<float4 *>(epi_addr(e, m, n)) = v;
+}
+
+// 128-bit read-only load that does not allocate in L1 (weights are streamed once per pass).
+__device__ __forceinline__ float4 ldg_stream4(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_stream4u(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+
+}  // namespace wgpt

@@ -1,0 +1,168 @@
+// Memory-bound row/elementwise kernels: residual add, GELU, LayerNorm, softmax, embedding gather,
+// arg-max, transposition. All are 128-bit vectorised where the shape allows.
+#pragma once
+#include "common.cuh"
+
+namespace wgpt {
+
+// out = a + b (elementWiseAddition, instructions.js:358-384), n4 float4 elements.
+__global__ void residual_kernel(const float4 *__restrict__ a, const float4 *__restrict__ b, float4 *__restrict__ out,
+                                size_t n4) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    float4 x = a[i], y = b[i];
+    out[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
+// GELU (instructions.js:705-748).
+__global__ void gelu_kernel(const float4 *__restrict__ in, float4 *__restrict__ out, size_t n4) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    float4 x = in[i];
+    out[i] = make_float4(gelu_f(x.x), gelu_f(x.y), gelu_f(x.z), gelu_f(x.w));
+  }
+}
+
+// LayerNorm, one warp per row (normStats + norm, instructions.js:451-550):
+// mean = sum/N, var = sum((x-mean)^2)/N, y = gamma*((x-mean)/sqrt(var+1e-5))+beta.
+// Row r of the input starts at in + r*ld_in (lets the caller normalise only the last row of each sequence).
+__global__ void layernorm_kernel(const float *__restrict__ in, size_t ld_in, const float *__restrict__ gamma,
+                                 const float *__restrict__ beta, float *__restrict__ out, size_t ld_out, int rows,
+                                 int N) {
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float4 *x = reinterpret_cast<const float4 *>(in + (size_t)row * ld_in);
+  int n4 = N >> 2;
+  float s = 0.f;
+  for (int i = lane; i < n4; i += 32) {
+    float4 v = x[i];
+    s += (v.x + v.y) + (v.z + v.w);
+  }
+  float mean = warp_sum(s) / (float)N;
+  float q = 0.f;
+  for (int i = lane; i < n4; i += 32) {
+    float4 v = x[i];
+    float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  float sd = sqrtf(warp_sum(q) / (float)N + 1e-5f);
+  const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
+  const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+  float4 *o = reinterpret_cast<float4 *>(out + (size_t)row * ld_out);
+  for (int i = lane; i < n4; i += 32) {
+    float4 v = x[i], g = g4[i], b = b4[i];
+    o[i] = make_float4(g.x * ((v.x - mean) / sd) + b.x, g.y * ((v.y - mean) / sd) + b.y,
+                       g.z * ((v.z - mean) / sd) + b.z, g.w * ((v.w - mean) / sd) + b.w);
+  }
+}
+
+// Row softmax, one warp per row (instructions.js:593-666). Scalar accesses: cols is arbitrary.
+__global__ void softmax_kernel(const float *__restrict__ in, float *__restrict__ out, int rows, int cols) {
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float *x = in + (size_t)row * cols;
+  float m = -3.402823e+38f;
+  for (int i = lane; i < cols; i += 32) m = fmaxf(m, x[i]);
+  m = warp_max(m);
+  float s = 0.f;
+  for (int i = lane; i < cols; i += 32) s += expf(x[i] - m);
+  s = warp_sum(s);
+  float *o = out + (size_t)row * cols;
+  for (int i = lane; i < cols; i += 32) o[i] = expf(x[i] - m) / s;
+}
+
+// Embedding gather + positional add (EmbedBlock, instructions.js:790-827) with ids on the device.
+// Row m = seq*n_tok + t reads wte[idx[m]] and wpe[*pos + t]. An id >= vocab sets *err and leaves zeros.
+__global__ void embed_kernel(const uint32_t *__restrict__ idx, const float *__restrict__ wte,
+                             const float *__restrict__ wpe, float *__restrict__ out, int rows, int n_tok, int E,
+                             int vocab, const int *__restrict__ pos, int *err) {
+  int m = blockIdx.x;
+  if (m >= rows) return;
+  uint32_t id = idx[m];
+  int t = m % n_tok;
+  int p = (pos ? *pos : 0) + t;
+  float4 *o = reinterpret_cast<float4 *>(out + (size_t)m * E);
+  if (id >= (uint32_t)vocab) {
+    if (threadIdx.x == 0) atomicExch(err, 1);
+    for (int i = threadIdx.x; i < E / 4; i += blockDim.x) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const float4 *a = reinterpret_cast<const float4 *>(wte + (size_t)id * E);
+  const float4 *b = reinterpret_cast<const float4 *>(wpe + (size_t)p * E);
+  for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
+    float4 x = a[i], y = b[i];
+    o[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
+// Greedy pick per sequence: arg-max of logits[seq, 0..V), lowest index on ties (globals.js:66-74
+// with top_k = 1). Writes the id as the next input token and into the output list at *step.
+__global__ void argmax_kernel(const float *__restrict__ logits, int V, uint32_t *__restrict__ next_ids,
+                              uint32_t *__restrict__ out_ids, int out_stride, const int *__restrict__ step) {
+  int seq = blockIdx.x;
+  const float *x = logits + (size_t)seq * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = x[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      if (bi == 0x7fffffff) bi = 0;  // all-NaN row: fall back to index 0 like an unsorted list head
+      next_ids[seq] = (uint32_t)bi;
+      if (out_ids) out_ids[(size_t)seq * out_stride + (step ? *step : 0)] = (uint32_t)bi;
+    }
+  }
+}
+
+// Advances the session's device-side position and step counters after a decode step.
+__global__ void advance_kernel(int *pos, int *step, int n_tok) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    *pos += n_tok;
+    *step += 1;
+  }
+}
+
+// out[c][r] = in[r][c] for an [R, C] matrix; 32x32 tiles through shared memory. Used once per weight at
+// load time (the reference transposes on the host, globals.js:80-94).
+__global__ void transpose_kernel(const float *__restrict__ in, float *__restrict__ out, int R, int C) {
+  __shared__ float tile[32][33];
+  int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < R && c < C) tile[j][threadIdx.x] = in[(size_t)r * C + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < R && c < C) out[(size_t)c * R + r] = tile[threadIdx.x][j];
+  }
+}
+
+}  // namespace wgpt

@@ -1,0 +1,132 @@
+// int8 weight-only dequant matmul, the kernel prototyped in other/int8-gemm.js:117-229.
+// Bq is [K, N/4] 32-bit words, byte j of word w in row k = column 4w+j (other/int8-gemm.js:36-42).
+// Integers are recovered exactly as the prototype does, (int32(word) << (24-8j)) >> 24 (:126-131); they are
+// exact in f32, the products accumulate in FP32, and the per-column scale multiplies the finished sum.
+// HBM-bound for small M: bytes = K*N (weights) + 4*M*K + 4*M*N + 4*N.
+#pragma once
+#include "common.cuh"
+
+namespace wgpt {
+
+__device__ __forceinline__ void unpack_int8x4(uint32_t word, float (&f)[4]) {
+  int32_t v = (int32_t)word;
+  f[0] = (float)((v << 24) >> 24);
+  f[1] = (float)((v << 16) >> 24);
+  f[2] = (float)((v << 8) >> 24);
+  f[3] = (float)(v >> 24);
+}
+
+// M <= 16 rows. Lane owns 4*VEC consecutive columns (VEC 32-bit words per load: VEC = 4 is a 128-bit load);
+// a warp covers 128*VEC columns of one k row; 8 warps x gridDim.y CTAs split K.
+// part: [gridDim.y][M][N] partial sums, summed (and scaled) by gemv_kn_reduce_kernel.
+template <int M, int VEC>
+__global__ void __launch_bounds__(256)
+int8_gemv_partial_kernel(const float *__restrict__ x, const uint32_t *__restrict__ Bq, int K, int N,
+                         float *__restrict__ part) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int CPL = 4 * VEC;  // columns per lane
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ksplit = gridDim.y;
+  const int kbeg = (int)(((long long)(K / 4) * blockIdx.y) / ksplit) * 4;
+  const int kend = (int)(((long long)(K / 4) * (blockIdx.y + 1)) / ksplit) * 4;
+  const int klen = kend - kbeg;
+  float *xs = smem;
+  float *red = smem + (size_t)M * klen;  // [8 warps][M][32 lanes][CPL]
+  for (int i = tid; i < M * klen; i += 256) {
+    int m = i / klen, k = i - m * klen;
+    xs[m * klen + k] = x[(size_t)m * K + kbeg + k];
+  }
+  __syncthreads();
+  const int n = (blockIdx.x * 32 + lane) * CPL;
+  const int ND4 = N >> 2;
+  float acc[M][CPL];
+#pragma unroll
+  for (int m = 0; m < M; m++)
+#pragma unroll
+    for (int c = 0; c < CPL; c++) acc[m][c] = 0.f;
+  if (n < N) {
+    const uint32_t *bp = Bq + (size_t)kbeg * ND4 + (n >> 2);
+#pragma unroll 4
+    for (int k = warp; k < klen; k += 8) {
+      uint32_t w[VEC];
+      if (VEC == 4) {
+        uint4 t = ldg_stream4u(reinterpret_cast<const uint4 *>(bp + (size_t)k * ND4));
+        w[0] = t.x; w[VEC > 1 ? 1 : 0] = t.y; w[VEC > 2 ? 2 : 0] = t.z; w[VEC > 3 ? 3 : 0] = t.w;
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; v++) w[v] = __ldg(bp + (size_t)k * ND4 + v);
+      }
+      float b[CPL];
+#pragma unroll
+      for (int v = 0; v < VEC; v++) {
+        float f[4];
+        unpack_int8x4(w[v], f);
+        b[4 * v] = f[0]; b[4 * v + 1] = f[1]; b[4 * v + 2] = f[2]; b[4 * v + 3] = f[3];
+      }
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float a = xs[m * klen + k];
+#pragma unroll
+        for (int c = 0; c < CPL; c++) acc[m][c] += a * b[c];
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < M; m++)
+#pragma unroll
+    for (int c = 0; c < CPL; c++) red[((warp * M + m) * 32 + lane) * CPL + c] = acc[m][c];
+  __syncthreads();
+  for (int i = tid; i < M * 32 * CPL; i += 256) {
+    int c = i % CPL, l = (i / CPL) % 32, m = i / (CPL * 32);
+    int nn = (blockIdx.x * 32 + l) * CPL + c;
+    if (nn >= N) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) s += red[((w * M + m) * 32 + l) * CPL + c];
+    part[((size_t)blockIdx.y * M + m) * N + nn] = s;
+  }
+}
+
+// General M: the 64x64x16 SIMT tile of gemm_simt_kernel with the B tile dequantised while it is staged.
+__global__ void __launch_bounds__(256)
+int8_gemm_simt_kernel(const float *__restrict__ A, const uint32_t *__restrict__ Bq, int M, int K, int N,
+                      Epilogue epi) {
+  __shared__ __align__(16) float As[16][64 + 4];
+  __shared__ __align__(16) float Bs[16][64 + 4];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, ND4 = N >> 2;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  const int a_row = tid >> 2, a_k4 = (tid & 3) * 4;
+  const int b_k = tid >> 4, b_w = tid & 15;  // 16 k x 16 words (64 columns)
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m0 + a_row < M && k0 + a_k4 < K) v = *reinterpret_cast<const float4 *>(A + (size_t)(m0 + a_row) * K + k0 + a_k4);
+    As[a_k4 + 0][a_row] = v.x; As[a_k4 + 1][a_row] = v.y; As[a_k4 + 2][a_row] = v.z; As[a_k4 + 3][a_row] = v.w;
+    float f[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 + b_k < K && n0 + b_w * 4 < N) unpack_int8x4(__ldg(Bq + (size_t)(k0 + b_k) * ND4 + (n0 >> 2) + b_w), f);
+    *reinterpret_cast<float4 *>(&Bs[b_k][b_w * 4]) = make_float4(f[0], f[1], f[2], f[3]);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      float4 a = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+      float4 b = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4]);
+      float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] += av[i] * bv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    int m = m0 + ty * 4 + i, n = n0 + tx * 4;
+    if (m < M && n < N) epi_store4(epi, make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), m, n);
+  }
+}
+
+}  // namespace wgpt

@@ -72,7 +72,7 @@ def make_weights(params, seed=1234, std=0.02, ln_random=False):
 
 
 def weight_list(params, weights):
-    """Weights in tensor_names order (the order the oracle's model takes)."""
+    """Weights in tensor_names order (the order tensor_names gives)."""
     return [weights[n] for n in tensor_names(params)]
 
 
