@@ -508,6 +508,15 @@ ORC_API int orc_kv_generate_greedy(orc_kv *s, const uint32_t *prompt, int n_prom
   return 0;
 }
 
+/* Caps the OpenMP team. A container may see every core of the host while being allowed only a few. */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

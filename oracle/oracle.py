@@ -26,11 +26,26 @@ def build(force=False):
     return so
 
 
+def usable_cores():
+    """Cores this process may really use: the affinity mask, further limited by a cgroup CPU quota."""
+    n = len(os.sched_getaffinity(0))
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            n = min(n, max(1, int(float(quota) / float(period))))
+    except Exception:
+        pass
+    return max(1, min(n, 64))
+
+
 def lib():
     global _LIB
     if _LIB is None:
+        # idle OpenMP workers must sleep, not spin: the team may be larger than the CPU share
+        os.environ.setdefault("OMP_WAIT_POLICY", "passive")
         _LIB = C.CDLL(build())
         L = _LIB
+        L.orc_set_threads(usable_cores())
         L.orc_gelu1.restype = C.c_float
         L.orc_gelu1.argtypes = [C.c_float]
         L.orc_model_create.restype = C.c_void_p

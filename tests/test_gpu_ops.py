@@ -148,9 +148,8 @@ def test_attention_known_answer(dev, ops):
 def test_int8_matmul(dev, oracle, M, K, N):
     from webgpt_b200 import _lib, synth
     A, q, packed, scales = synth.make_int8_case(M, K, N)
-    out = dev.buffer(M * N * 4)
-    _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, dev.tensor(A).ptr, dev.tensor(packed).ptr,
-              dev.tensor(scales).ptr, out.ptr)
+    out, a_d, b_d, s_d = dev.buffer(M * N * 4), dev.tensor(A), dev.tensor(packed), dev.tensor(scales)
+    _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, a_d.ptr, b_d.ptr, s_d.ptr, out.ptr)
     got = out.read(np.float32, M * N).reshape(M, N)
     assert rel_err(got, oracle.int8_matmul(A, packed, scales, N)) < TOL
     assert np.max(np.abs(got - oracle.int8_matmul(A, packed, scales, N, literal=True))) < 0.1  # int8-gemm.js:321
@@ -167,8 +166,7 @@ def test_int8_unpack_bit_exact(dev, K):
     packed = np.ascontiguousarray(q).view(np.uint32).reshape(K, N // 4)
     for M in (1, K if K <= 16 else 16, K):
         A = np.eye(K, dtype=np.float32)[:M]
-        out = dev.buffer(M * N * 4)
-        _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, dev.tensor(A).ptr, dev.tensor(packed).ptr,
-                  dev.tensor(np.ones(N, np.float32)).ptr, out.ptr)
+        out, a_d, b_d, s_d = dev.buffer(M * N * 4), dev.tensor(A), dev.tensor(packed), dev.tensor(np.ones(N, np.float32))
+        _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, a_d.ptr, b_d.ptr, s_d.ptr, out.ptr)
         got = out.read(np.float32, M * N).reshape(M, N)
         assert np.array_equal(got, q[:M].astype(np.float32))

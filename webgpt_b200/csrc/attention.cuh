@@ -37,22 +37,28 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
 
   float m = -INFINITY, l = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  // The trip count is the same for every lane of the warp (the shuffles below name all 32 lanes); a group whose
+  // position falls past the end of the slice runs the iteration with `valid` false and contributes nothing.
 #pragma unroll 2
-  for (int j = beg + warp * G + g; j < end; j += 4 * G) {
-    float4 k4 = *reinterpret_cast<const float4 *>(kb + (size_t)j * ldkv);
-    float4 v4 = *reinterpret_cast<const float4 *>(vb + (size_t)j * ldkv);
+  for (int j0 = beg + warp * G; j0 < end; j0 += 4 * G) {
+    const int j = j0 + g;
+    const bool valid = j < end;
+    const int jj = valid ? j : end - 1;  // in-bounds address for the idle group
+    float4 k4 = *reinterpret_cast<const float4 *>(kb + (size_t)jj * ldkv);
+    float4 v4 = *reinterpret_cast<const float4 *>(vb + (size_t)jj * ldkv);
     float s = dot4(q4, k4);
 #pragma unroll
     for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    s *= scale;
-    float mn = fmaxf(m, s);
-    float corr = expf(m - mn), p = expf(s - mn);  // m = -inf on the first key: corr = 0
-    l = l * corr + p;
-    acc.x = acc.x * corr + p * v4.x; acc.y = acc.y * corr + p * v4.y;
-    acc.z = acc.z * corr + p * v4.z; acc.w = acc.w * corr + p * v4.w;
-    m = mn;
+    if (valid) {
+      s *= scale;
+      float mn = fmaxf(m, s);
+      float corr = expf(m - mn), p = expf(s - mn);  // m = -inf on the first key: corr = 0
+      l = l * corr + p;
+      acc.x = acc.x * corr + p * v4.x; acc.y = acc.y * corr + p * v4.y;
+      acc.z = acc.z * corr + p * v4.z; acc.w = acc.w * corr + p * v4.w;
+      m = mn;
+    }
   }
-  // A loop with a lane-dependent trip count ends with the groups of a warp diverged; re-converge.
   __syncwarp();
   // merge the G groups of the warp
 #pragma unroll

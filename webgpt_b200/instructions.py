@@ -61,8 +61,14 @@ class Block:
         self.destroyBuffers()
 
     def _compute(self, fn, *args):
+        """A compute pass. Buffer arguments are held by the pass (as a bind group holds its buffers in the
+        reference) and resolved to device addresses when the pass runs."""
         dev = self.device
-        return {"flag": "compute", "run": lambda: _lib.call(fn, dev.handle, *args)}
+
+        def run():
+            _lib.call(fn, dev.handle, *[a.ptr if hasattr(a, "ptr") else a for a in args])
+
+        return {"flag": "compute", "run": run, "buffers": [a for a in args if hasattr(a, "ptr")]}
 
 
 class FastMatMulBlockClass(Block):
@@ -75,10 +81,10 @@ class FastMatMulBlockClass(Block):
         if cols % 8 != 0:
             raise ValueError("Cols must be divisible by 16.")
         resultBuffer = self.initResultBuffer([rows, cols])
-        bias = biasBuffer.ptr if biasBuffer is not None else None
+        bias = biasBuffer
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_matmul", rows, cols, shared, inputBuffer.ptr, weightsBuffer.ptr, bias,
-                                         resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_matmul", rows, cols, shared, inputBuffer, weightsBuffer, bias,
+                                         resultBuffer)]}
 
 
 class ResidualBlockClass(Block):
@@ -92,7 +98,7 @@ class ResidualBlockClass(Block):
             raise ValueError("Cols must be divisible by 4.")
         resultBuffer = self.initResultBuffer([rows, cols])
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_residual", rows, cols, outputBuf.ptr, residualBuf.ptr, resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_residual", rows, cols, outputBuf, residualBuf, resultBuffer)]}
 
 
 class LayerNormBlockClass(Block):
@@ -106,8 +112,8 @@ class LayerNormBlockClass(Block):
             raise ValueError("Cols must be divisible by 4.")
         resultBuffer = self.initResultBuffer([rows, cols])
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_layernorm", rows, cols, inputBuffer.ptr, gammaBuffer.ptr, betaBuffer.ptr,
-                                         resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_layernorm", rows, cols, inputBuffer, gammaBuffer, betaBuffer,
+                                         resultBuffer)]}
 
 
 class SoftmaxBlockClass(Block):
@@ -121,7 +127,7 @@ class SoftmaxBlockClass(Block):
             raise NotImplementedError("transposed softmax output is not used by the model path")
         resultBuffer = self.initResultBuffer([rows, cols])
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_softmax", rows, cols, inputBuffer.ptr, resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_softmax", rows, cols, inputBuffer, resultBuffer)]}
 
 
 class GeluBlockClass(Block):
@@ -135,7 +141,7 @@ class GeluBlockClass(Block):
             raise ValueError("Cols must be divisible by 4.")
         resultBuffer = self.initResultBuffer([rows, cols])
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_gelu", rows, cols, inputBuf.ptr, resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_gelu", rows, cols, inputBuf, resultBuffer)]}
 
 
 class EmbedBlockClass(Block):
@@ -155,8 +161,8 @@ class EmbedBlockClass(Block):
         ids.write(np.asarray(idx, dtype=np.uint32)[:seq_length])
         resultBuffer = self.initResultBuffer([seq_length, n_embd])
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_embed", ids.ptr, seq_length, n_embd, vocab_chunk_size,
-                                         embdBuffers[0].ptr, posEmbdBuffer.ptr, resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_embed", ids, seq_length, n_embd, vocab_chunk_size,
+                                         embdBuffers[0], posEmbdBuffer, resultBuffer)]}
 
 
 class DeEmbedBlockClass(Block):
@@ -171,8 +177,8 @@ class DeEmbedBlockClass(Block):
             raise ValueError("embeddings are loaded as one chunk")
         resultBuffer = self.initBuffer(["map_read", "copy_to"], [vocab_size], f"logits_{vocab_size}")
         return {"resultBuffer": resultBuffer,
-                "passes": [self._compute("wgpt_deembed", n_embd, vocab_size, seq_length, embedBuffer.ptr,
-                                         deEmbeddingsBuffers[0].ptr, resultBuffer.ptr)]}
+                "passes": [self._compute("wgpt_deembed", n_embd, vocab_size, seq_length, embedBuffer,
+                                         deEmbeddingsBuffers[0], resultBuffer)]}
 
 
 class AttentionBlockClass(Block):
@@ -187,6 +193,6 @@ class AttentionBlockClass(Block):
         resultBuffer = self.initResultBuffer([seq_length, n_embd])
         return {"resultBuffer": resultBuffer,
                 "passes": [self._compute("wgpt_attention", seq_length, n_embd, float(attentionDotProductScale), n_head,
-                                         head_size, inputBuffer.ptr, qWeightsBuffer.ptr, qBiasBuffer.ptr,
-                                         kWeightsBuffer.ptr, kBiasBuffer.ptr, vWeightsBuffer.ptr, vBiasBuffer.ptr,
-                                         linearWeightsBuffer.ptr, linearBiasBuffer.ptr, resultBuffer.ptr)]}
+                                         head_size, inputBuffer, qWeightsBuffer, qBiasBuffer,
+                                         kWeightsBuffer, kBiasBuffer, vWeightsBuffer, vBiasBuffer,
+                                         linearWeightsBuffer, linearBiasBuffer, resultBuffer)]}
