@@ -95,6 +95,25 @@ int32_t wgpt_event_destroy(wgpt_device *dev, void *event);
 int32_t wgpt_matmul(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in, const float *W,
                     const float *bias, float *out);
 
+/* No counterpart in the reference. The same product as wgpt_matmul for 1..8 rows, for callers that must not
+ * trigger a device allocation: an inference server that has handed all of HBM to its own arena and treats any
+ * later cudaMalloc as a budget violation, a latency-critical decode loop (cudaMalloc can serialise against every
+ * stream of the device), or a plugin host that forbids driver allocations once it is serving. wgpt_matmul may
+ * grow a library-owned workspace for its split-K partial sums; this entry point keeps them in an array compiled
+ * into the library (WGPT_STATIC_SCRATCH_FLOATS floats = 8 MiB per GPU that loads the library, held until
+ * exit) and calls no allocating routine.
+ *  - Limits: rows <= 8 and rows * cols <= WGPT_STATIC_SCRATCH_FLOATS, otherwise WGPT_ERR_SHAPE; all other
+ *    preconditions are those of wgpt_matmul. When the usual K split does not fit the array a smaller split is
+ *    used, so results may differ from wgpt_matmul in the last bits (different summation order).
+ *  - The first call on each device looks up the array's device address; make that first call outside any
+ *    stream capture.
+ *  - All calls on one GPU share the array (it keeps the previous call's partial sums; every call overwrites all
+ *    it reads, nothing needs clearing). Calls on the same wgpt_device are stream-ordered and safe; calls that
+ *    can overlap on one GPU (two wgpt_device handles on the same ordinal) race on it. */
+#define WGPT_STATIC_SCRATCH_FLOATS 2097152
+int32_t wgpt_matmul_static(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in,
+                           const float *W, const float *bias, float *out);
+
 /* ResidualBlock.newInstance(rows, cols, outputBuf, residualBuf) (instructions.js:336-356; kernel :358-384).
  * cols % 4 == 0 (:337). out may alias a or b. */
 int32_t wgpt_residual(wgpt_device *dev, int32_t rows, int32_t cols, const float *a, const float *b, float *out);

@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -1060,4 +1061,51 @@ WGPT_EXPORT int32_t wgpt_session_tap(wgpt_session *s, float *dst, uint64_t max_f
   CK(cudaMemcpyAsync(dst, s->x, n * 4, cudaMemcpyDeviceToDevice, s->m->dev->stream));
   if (floats_written) *floats_written = n;
   return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ matmul without allocation
+// Split-K partial sums of wgpt_matmul_static live here instead of in the device workspace that wgpt_matmul
+// grows with cudaMalloc. The array is part of the loaded module: every GPU that loads this library holds these
+// 8 MiB until the process exits. In host code the name below is only a handle for the runtime's symbol table,
+// never a device address; the address is looked up once per device with cudaGetSymbolAddress and that pointer is
+// what the kernels receive.
+static __device__ __align__(256) float g_static_scratch[WGPT_STATIC_SCRATCH_FLOATS];
+static std::mutex g_static_mu;
+static float *g_static_scratch_ptr[64];  // per device ordinal, filled on first use
+
+static int32_t static_scratch_for(wgpt_device *dev, float **out) {
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64, WGPT_ERR_UNSUPPORTED, "device ordinal %d not supported", dev->ordinal);
+  if (g_static_scratch_ptr[dev->ordinal] == nullptr) {
+    float *p = nullptr;
+    CK(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch));  // dev is the current device
+    REQUIRE(p != nullptr, WGPT_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_ptr[dev->ordinal] = p;
+  }
+  *out = g_static_scratch_ptr[dev->ordinal];
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_matmul_static(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in,
+                                       const float *W, const float *bias, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && W && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1 && shared >= 1, WGPT_ERR_SHAPE, "empty matmul %dx%dx%d", rows, cols, shared);
+  REQUIRE(cols % 8 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 16.");
+  REQUIRE(shared % 4 == 0, WGPT_ERR_SHAPE, "shared dimension %d must be divisible by 4", shared);
+  REQUIRE(aligned16(in) && aligned16(W) && aligned16(out) && aligned16(bias), WGPT_ERR_ALIGN,
+          "buffers must be 16-byte aligned");
+  REQUIRE(rows <= 8, WGPT_ERR_SHAPE, "wgpt_matmul_static handles at most 8 rows, got %d", rows);
+  const size_t per_slice = (size_t)rows * cols;
+  REQUIRE(per_slice <= WGPT_STATIC_SCRATCH_FLOATS, WGPT_ERR_SHAPE,
+          "rows*cols = %zu exceeds the built-in scratch of %u floats; use wgpt_matmul", per_slice,
+          (unsigned)WGPT_STATIC_SCRATCH_FLOATS);
+  int ksplit = kn_ksplit(dev, shared, (cols + 127) / 128);
+  const size_t fit = WGPT_STATIC_SCRATCH_FLOATS / per_slice;  // >= 1
+  if ((size_t)ksplit > fit) ksplit = (int)fit;
+  float *part = nullptr;
+  TRY(static_scratch_for(dev, &part));
+  // Every element of the [ksplit][rows][cols] partial block is written by the first kernel before the second
+  // reads it, so nothing left over from an earlier call is ever read and nothing needs clearing.
+  return gemv_kn_with_scratch(dev, rows, in, W, shared, cols, ksplit, part, plain_epi(out, cols, bias));
 }
