@@ -66,6 +66,8 @@ struct wgpt_device {
   void *scratch;  // library-owned workspace (split-K partial sums, temporaries of wgpt_attention)
   size_t scratch_cap;
   int *d_err;     // device-side error word (out-of-range token id)
+  bool pdl;       // launch the decode-chain kernels with programmatic dependent launch (WGPT_PDL=0 turns it off)
+  bool graphs;    // replay decode steps as a CUDA graph (WGPT_GRAPH=0 turns it off)
 };
 
 #define LAUNCH(dev, kernel, grid, block, smem, ...)                       \
@@ -73,6 +75,31 @@ struct wgpt_device {
     kernel<<<(grid), (block), (smem), (dev)->stream>>>(__VA_ARGS__);      \
     (dev)->launches++;                                                    \
     CK(cudaGetLastError());                                               \
+  } while (0)
+
+// Launch for kernels that call pdl_wait() before touching anything an earlier kernel wrote: with dev->pdl they
+// carry the programmatic-serialisation attribute and may start while their predecessor is still running.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_ex(bool pdl, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define LAUNCH_PDL(dev, kernel, grid, block, smem, ...)                                          \
+  do {                                                                                           \
+    CK(launch_ex((dev)->pdl, (dev)->stream, kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__)); \
+    (dev)->launches++;                                                                           \
   } while (0)
 
 static int32_t use(wgpt_device *dev) {
@@ -118,6 +145,10 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->scratch = nullptr;
   dev->scratch_cap = 0;
   dev->d_err = nullptr;
+  const char *ev = getenv("WGPT_PDL");
+  dev->pdl = !(ev && ev[0] == '0');
+  ev = getenv("WGPT_GRAPH");
+  dev->graphs = !(ev && ev[0] == '0');
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&dev->d_err, sizeof(int));
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream);
@@ -264,7 +295,10 @@ static int32_t launch_gemv_nk_t(wgpt_device *dev, const float *x, size_t ldx, co
   auto kern = gemv_nk_kernel<M, WK, CPW>;
   if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = (N + WC * CPW - 1) / (WC * CPW);
-  LAUNCH(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi);
+  // Weight slices are pulled towards L2 ahead of the dependency wait unless the matrix would flush L2 (the
+  // de-embedding table is larger than L2 and is long enough to be bandwidth-bound on its own).
+  int prefetch = (size_t)N * K * 4 <= (size_t(32) << 20) ? 1 : 0;
+  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi, prefetch);
   return WGPT_OK;
 }
 
@@ -394,8 +428,8 @@ static int32_t launch_attn_decode(wgpt_device *dev, int hs, const float *q, int 
   dim3 grid(H, n_seq, n_split);
 #define CASE(HSV)                                                                                             \
   case HSV:                                                                                                   \
-    LAUNCH(dev, attn_decode_kernel<HSV>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
-           part, counters);                                                                                   \
+    LAUNCH_PDL(dev, attn_decode_kernel<HSV>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
+               part, counters);                                                                                   \
     return WGPT_OK;
   switch (hs) {
     CASE(4) CASE(8) CASE(16) CASE(32) CASE(64) CASE(128)
@@ -485,8 +519,8 @@ WGPT_EXPORT int32_t wgpt_embed(wgpt_device *dev, const uint32_t *idx, int32_t se
   REQUIRE(seq_length >= 1 && vocab_size >= 1, WGPT_ERR_SHAPE, "empty embed");
   REQUIRE(n_embd >= 4 && n_embd % 4 == 0, WGPT_ERR_SHAPE, "n_embd must be divisible by 4.");
   REQUIRE(aligned16(wte) && aligned16(wpe) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
-  LAUNCH(dev, embed_kernel, seq_length, 128, 0, idx, wte, wpe, out, seq_length, seq_length, n_embd, vocab_size,
-         (const int *)nullptr, dev->d_err);
+  LAUNCH_PDL(dev, embed_kernel, seq_length, 128, 0, idx, wte, wpe, out, seq_length, seq_length, n_embd, vocab_size,
+             (const int *)nullptr, dev->d_err);
   return check_err_word(dev, "wgpt_embed");
 }
 
@@ -745,7 +779,12 @@ struct wgpt_session {
   std::vector<uint32_t> prompts;  // host copy, [n_seq][n_prompt]
   int n_prompt, n_generated;
   bool ids_dirty;  // s->ids no longer holds the prompt window
+  cudaGraphExec_t step_graph;  // one captured decode step (pointers of this session baked in)
+  uint64_t step_graph_launches;
+  bool step_warm;
 };
+
+static void drop_step_graph(wgpt_session *s);
 
 static void session_free_act(wgpt_session *s) {
   cudaFree(s->x); cudaFree(s->h); cudaFree(s->q); cudaFree(s->o); cudaFree(s->f); cudaFree(s->ids);
@@ -757,6 +796,7 @@ static int32_t session_reserve(wgpt_session *s, int n_tok) {
   if (n_tok <= s->cap_tok) return WGPT_OK;
   wgpt_device *dev = s->m->dev;
   CK(cudaStreamSynchronize(dev->stream));
+  drop_step_graph(s);  // the captured step holds the old buffer addresses
   session_free_act(s);
   s->cap_tok = 0;
   size_t M = (size_t)s->n_seq * n_tok, E = s->m->p.n_embd;
@@ -783,10 +823,10 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   if (e == cudaSuccess) e = cudaMalloc(&s->vc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->logits, (size_t)n_seq * p.vocab_size * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 2) * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, (size_t)n_seq * p.n_head * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, ((size_t)n_seq * p.n_head + 1) * 4);  // + arg-max done counter
   if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->d_pos, 2 * sizeof(int));
-  if (e == cudaSuccess) e = cudaMemsetAsync(s->attn_cnt, 0, (size_t)n_seq * p.n_head * 4, m->dev->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s->attn_cnt, 0, ((size_t)n_seq * p.n_head + 1) * 4, m->dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), m->dev->stream);
   if (e != cudaSuccess) {
     cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
@@ -804,6 +844,7 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
   TRY(use(s->m->dev));
   cudaStreamSynchronize(s->m->dev->stream);
+  drop_step_graph(s);
   session_free_act(s);
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
   cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos);
@@ -834,7 +875,8 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok) {
   const int E = p.n_embd, F = 4 * E, H = p.n_head, hs = m->hs, M = s->n_seq * n_tok;
   const size_t kv_layer = (size_t)s->n_seq * p.n_ctx * E;
 
-  LAUNCH(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size, s->d_pos, dev->d_err);
+  LAUNCH_PDL(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size,
+             (const int *)s->d_pos, dev->d_err);
 
   auto mm = [&](const float *a, const float *gamma, const float *beta, const float *Wt, int K, int N,
                 const Epilogue &e) -> int32_t {
@@ -895,7 +937,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok) {
 }
 
 static int32_t advance(wgpt_session *s, int n_tok) {
-  LAUNCH(s->m->dev, advance_kernel, 1, 32, 0, s->d_pos, s->d_step, n_tok);
+  LAUNCH_PDL(s->m->dev, advance_kernel, 1, 32, 0, s->d_pos, s->d_step, n_tok);
   s->len += n_tok;
   return WGPT_OK;
 }
@@ -935,6 +977,7 @@ WGPT_EXPORT int32_t wgpt_model_run(wgpt_session *s, const uint32_t *idx_host, in
 static int32_t reserve_out_ids(wgpt_session *s, int n_new) {
   if (n_new <= s->out_cap) return WGPT_OK;
   CK(cudaStreamSynchronize(s->m->dev->stream));
+  drop_step_graph(s);  // out_ids and its stride are baked into the captured step
   cudaFree(s->out_ids);
   s->out_ids = nullptr;
   s->out_cap = 0;
@@ -943,10 +986,62 @@ static int32_t reserve_out_ids(wgpt_session *s, int n_new) {
   return WGPT_OK;
 }
 
-static int32_t pick(wgpt_session *s) {
-  LAUNCH(s->m->dev, argmax_kernel, s->n_seq, 1024, 0, s->logits, s->m->p.vocab_size, s->next_ids, s->out_ids,
-         s->out_cap, s->d_step);
+// Arg-max of the newest logits of every sequence -> next input ids and output list; the same kernel then advances
+// the session's position by n_tok and its step counter by one.
+static int32_t pick_and_advance(wgpt_session *s, int n_tok) {
+  LAUNCH_PDL(s->m->dev, argmax_kernel, s->n_seq, 1024, 0, (const float *)s->logits, s->m->p.vocab_size, s->next_ids,
+             s->out_ids, s->out_cap, s->d_pos, s->d_step, n_tok, s->attn_cnt + (size_t)s->n_seq * s->m->p.n_head);
+  s->len += n_tok;
   return WGPT_OK;
+}
+
+// One decode step (newest token of every sequence -> next token), replayed as a CUDA graph: all position- and
+// step-dependent values are read from device memory, so one captured step serves every position.
+static int32_t decode_step(wgpt_session *s) {
+  wgpt_device *dev = s->m->dev;
+  if (!dev->graphs) {
+    TRY(forward(s, s->next_ids, 1));
+    return pick_and_advance(s, 1);
+  }
+  if (s->step_graph == nullptr) {
+    // The first step runs eagerly (it also sets every kernel's shared-memory attribute); the second is captured.
+    if (!s->step_warm) {
+      s->step_warm = true;
+      TRY(forward(s, s->next_ids, 1));
+      return pick_and_advance(s, 1);
+    }
+    uint64_t before = dev->launches;
+    int len_before = s->len;
+    cudaGraph_t graph = nullptr;
+    CK(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed));
+    int32_t rc = forward(s, s->next_ids, 1);
+    if (rc == WGPT_OK) rc = pick_and_advance(s, 1);
+    cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
+    s->len = len_before;  // capturing enqueued nothing
+    s->step_graph_launches = dev->launches - before;
+    dev->launches = before;
+    if (rc != WGPT_OK) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    if (e != cudaSuccess) return fail(WGPT_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&s->step_graph, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+      s->step_graph = nullptr;
+      return fail(WGPT_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+  }
+  CK(cudaGraphLaunch(s->step_graph, dev->stream));
+  dev->launches += s->step_graph_launches;
+  s->len += 1;
+  return WGPT_OK;
+}
+
+static void drop_step_graph(wgpt_session *s) {
+  if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
+  s->step_graph = nullptr;
+  s->step_warm = false;
 }
 
 // Host copy of the prompts (needed again only if the window slides) and their device copy.
@@ -994,13 +1089,10 @@ WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
     s->ids_dirty = false;
   }
   TRY(forward(s, s->ids, first));
-  TRY(pick(s));
-  TRY(advance(s, first));
+  TRY(pick_and_advance(s, first));
   for (int i = 1; i < n_new; i++) {
     if (s->len + 1 <= n_ctx) {
-      TRY(forward(s, s->next_ids, 1));
-      TRY(pick(s));
-      TRY(advance(s, 1));
+      TRY(decode_step(s));
       continue;
     }
     // Window slides: every position index shifts, so the cache is void; recompute the newest n_ctx tokens
@@ -1021,8 +1113,7 @@ WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
     CK(cudaMemcpyAsync(s->ids, window.data(), window.size() * 4, cudaMemcpyHostToDevice, dev->stream));
     s->ids_dirty = true;
     TRY(forward(s, s->ids, n_ctx));
-    TRY(pick(s));
-    TRY(advance(s, n_ctx));
+    TRY(pick_and_advance(s, n_ctx));
     CK(cudaStreamSynchronize(dev->stream));  // `window` is pageable host memory about to go out of scope
   }
   s->n_generated = n_new;

@@ -27,11 +27,13 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
   const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, n_split = gridDim.z, H = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane / LPP, lig = lane % LPP;
-  const int L = *pos + 1;
+  pdl_launch_dependents();
+  pdl_wait();  // q, the cache row of this step and *pos come from earlier kernels
+  const int L = __ldcg(pos) + 1;
   const int chunk = (L + n_split - 1) / n_split;
   const int beg = split * chunk, end = min(L, beg + chunk);
 
-  const float4 q4 = *reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4);
+  const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4));
   const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
   const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
 
@@ -44,8 +46,8 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     const int j = j0 + g;
     const bool valid = j < end;
     const int jj = valid ? j : end - 1;  // in-bounds address for the idle group
-    float4 k4 = *reinterpret_cast<const float4 *>(kb + (size_t)jj * ldkv);
-    float4 v4 = *reinterpret_cast<const float4 *>(vb + (size_t)jj * ldkv);
+    float4 k4 = __ldcg(reinterpret_cast<const float4 *>(kb + (size_t)jj * ldkv));
+    float4 v4 = __ldcg(reinterpret_cast<const float4 *>(vb + (size_t)jj * ldkv));
     float s = dot4(q4, k4);
 #pragma unroll
     for (int o = LPP / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);

@@ -39,7 +39,7 @@ __device__ __forceinline__ float *epi_addr(const Epilogue &e, int m, int n) {
   int sec = n >= 2 * e.E ? 2 : 1;
   int c = n - sec * e.E;
   int seq = m / e.n_tok, t = m - seq * e.n_tok;
-  size_t row = (size_t)seq * e.n_ctx + (size_t)(*e.pos) + t;
+  size_t row = (size_t)seq * e.n_ctx + (size_t)__ldcg(e.pos) + t;
   return (sec == 1 ? e.kc : e.vc) + row * e.E + c;
 }
 
@@ -47,7 +47,7 @@ __device__ __forceinline__ float epi_apply(const Epilogue &e, float v, int m, in
   if (e.colscale) v *= e.colscale[n];
   if (e.bias) v += e.bias[n];
   if (e.act == 1) v = gelu_f(v);
-  if (e.residual) v += e.residual[(size_t)m * e.ld + n];
+  if (e.residual) v += __ldcg(e.residual + (size_t)m * e.ld + n);
   return v;
 }
 
@@ -66,7 +66,7 @@ __device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, i
   }
   if (e.act == 1) { v.x = gelu_f(v.x); v.y = gelu_f(v.y); v.z = gelu_f(v.z); v.w = gelu_f(v.w); }
   if (e.residual) {
-    float4 r = *reinterpret_cast<const float4 *>(e.residual + (size_t)m * e.ld + n);
+    float4 r = __ldcg(reinterpret_cast<const float4 *>(e.residual + (size_t)m * e.ld + n));
     v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
   }
   *reinterpret_cast<float4 *>(epi_addr(e, m, n)) = v;
@@ -86,6 +86,23 @@ __device__ __forceinline__ uint4 ldg_stream4u(const uint4 *p) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
+}
+
+// Activations written by an earlier kernel are read with __ldcg (L2, bypassing L1) in every kernel that can be
+// launched programmatically: such a kernel becomes resident, and has its SM's L1 invalidated, while its
+// predecessor is still running, so a line another CTA of the predecessor pulled into that L1 afterwards (for
+// instance around an in-place residual update) would otherwise be read stale after the wait.
+//
+// Programmatic dependent launch. A kernel launched with the programmatic-serialisation attribute may start
+// while its predecessor in the stream is still running; everything it does before pdl_wait() must therefore
+// touch only data no earlier kernel writes (here: weights). pdl_wait() returns once every earlier kernel has
+// completed and its writes are visible; without the attribute both calls are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Asks the memory system to bring [p, p+bytes) into L2 (p 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

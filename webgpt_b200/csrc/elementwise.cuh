@@ -83,9 +83,11 @@ __global__ void embed_kernel(const uint32_t *__restrict__ idx, const float *__re
                              int vocab, const int *__restrict__ pos, int *err) {
   int m = blockIdx.x;
   if (m >= rows) return;
-  uint32_t id = idx[m];
+  pdl_launch_dependents();
+  pdl_wait();  // idx and *pos are written by the previous step's arg-max
+  uint32_t id = __ldcg(idx + m);
   int t = m % n_tok;
-  int p = (pos ? *pos : 0) + t;
+  int p = (pos ? __ldcg(pos) : 0) + t;
   float4 *o = reinterpret_cast<float4 *>(out + (size_t)m * E);
   if (id >= (uint32_t)vocab) {
     if (threadIdx.x == 0) atomicExch(err, 1);
@@ -101,15 +103,21 @@ __global__ void embed_kernel(const uint32_t *__restrict__ idx, const float *__re
 }
 
 // Greedy pick per sequence: arg-max of logits[seq, 0..V), lowest index on ties (globals.js:66-74
-// with top_k = 1). Writes the id as the next input token and into the output list at *step.
+// with top_k = 1). Writes the id as the next input token and into the output list at *step. The last block to
+// finish then advances the session's position by n_tok and its step counter by one (every block has read
+// *step before it can be counted as finished). done_counter must be zero on entry and is left zero.
 __global__ void argmax_kernel(const float *__restrict__ logits, int V, uint32_t *__restrict__ next_ids,
-                              uint32_t *__restrict__ out_ids, int out_stride, const int *__restrict__ step) {
+                              uint32_t *__restrict__ out_ids, int out_stride, int *__restrict__ pos,
+                              int *__restrict__ step, int n_tok, unsigned int *__restrict__ done_counter) {
+  pdl_launch_dependents();
+  pdl_wait();
   int seq = blockIdx.x;
+  const int my_step = __ldcg(step);
   const float *x = logits + (size_t)seq * V;
   float best = -INFINITY;
   int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = x[i];
+    float v = __ldcg(x + i);
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
   __shared__ float sv[32];
@@ -134,18 +142,26 @@ __global__ void argmax_kernel(const float *__restrict__ logits, int V, uint32_t 
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
     if (lane == 0) {
-      if (bi == 0x7fffffff) bi = 0;  // all-NaN row: fall back to index 0 like an unsorted list head
+      if (bi == 0x7fffffff) bi = 0;  // a row of NaNs compares false everywhere: report index 0
       next_ids[seq] = (uint32_t)bi;
-      if (out_ids) out_ids[(size_t)seq * out_stride + (step ? *step : 0)] = (uint32_t)bi;
+      if (out_ids) out_ids[(size_t)seq * out_stride + my_step] = (uint32_t)bi;
+      __threadfence();
+      unsigned int prev = atomicAdd(done_counter, 1u);
+      if (prev == gridDim.x - 1) {
+        *pos = __ldcg(pos) + n_tok;
+        *step = my_step + 1;
+        *done_counter = 0u;
+      }
     }
   }
 }
 
 // Advances the session's device-side position and step counters after a decode step.
 __global__ void advance_kernel(int *pos, int *step, int n_tok) {
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
-    *pos += n_tok;
-    *step += 1;
+    *pos = __ldcg(pos) + n_tok;
+    *step = __ldcg(step) + 1;
   }
 }
 

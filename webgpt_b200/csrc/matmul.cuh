@@ -19,7 +19,8 @@ namespace wgpt {
 template <int M, int WK, int CPW>
 __global__ void __launch_bounds__(256)
 gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
-               const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, Epilogue epi) {
+               const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, Epilogue epi,
+               int prefetch) {
   extern __shared__ __align__(16) float smem[];
   float *xs = smem;
   float *red = smem + (size_t)M * K;
@@ -28,17 +29,32 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
   constexpr int WC = 8 / WK;
   const int wc = warp / WK, wk = warp % WK;
   const int col0 = (blockIdx.x * WC + wc) * CPW;
+  const int beg = (int)(((long long)K4 * wk) / WK), end = (int)(((long long)K4 * (wk + 1)) / WK);
+  const float4 *w4[CPW];
+#pragma unroll
+  for (int c = 0; c < CPW; c++) {
+    int col = col0 + c < N ? col0 + c : N - 1;  // clamp: out-of-range columns read a valid row, never stored
+    w4[c] = reinterpret_cast<const float4 *>(Wt + (size_t)col * K);
+  }
+  // ---- before the dependency wait: let the next kernel start, and pull this warp's weight slice (which no
+  // kernel writes) towards L2 so that the HBM stream does not stop at the kernel boundary ----
+  pdl_launch_dependents();
+  if (prefetch && lane == 0 && end > beg) {
+#pragma unroll
+    for (int c = 0; c < CPW; c++) prefetch_l2(w4[c] + beg, (uint32_t)(end - beg) * 16u);
+  }
+  pdl_wait();
 
   // ---- stage the input rows; one warp per row does the LayerNorm (instructions.js:451-550) ----
   for (int m = warp; m < M; m += 8) {
     const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)m * ldx);
     float4 *dst = reinterpret_cast<float4 *>(xs + (size_t)m * K);
     if (gamma == nullptr) {
-      for (int i = lane; i < K4; i += 32) dst[i] = src[i];
+      for (int i = lane; i < K4; i += 32) dst[i] = __ldcg(src + i);
     } else {
       float s = 0.f;
       for (int i = lane; i < K4; i += 32) {
-        float4 v = src[i];
+        float4 v = __ldcg(src + i);
         dst[i] = v;
         s += (v.x + v.y) + (v.z + v.w);
       }
@@ -68,13 +84,6 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
 #pragma unroll
     for (int m = 0; m < M; m++) acc[c][m] = 0.f;
 
-  const int beg = (int)(((long long)K4 * wk) / WK), end = (int)(((long long)K4 * (wk + 1)) / WK);
-  const float4 *w4[CPW];
-#pragma unroll
-  for (int c = 0; c < CPW; c++) {
-    int col = col0 + c < N ? col0 + c : N - 1;  // clamp: out-of-range columns read a valid row, never stored
-    w4[c] = reinterpret_cast<const float4 *>(Wt + (size_t)col * K);
-  }
   const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
 #pragma unroll 4
   for (int i = beg + lane; i < end; i += 32) {
