@@ -68,6 +68,7 @@ struct wgpt_device {
   int *d_err;     // device-side error word (out-of-range token id)
   bool pdl;       // launch the decode-chain kernels with programmatic dependent launch (WGPT_PDL=0 turns it off)
   bool graphs;    // replay decode steps as a CUDA graph (WGPT_GRAPH=0 turns it off)
+  bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
 };
 
 #define LAUNCH(dev, kernel, grid, block, smem, ...)                       \
@@ -149,6 +150,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->pdl = !(ev && ev[0] == '0');
   ev = getenv("WGPT_GRAPH");
   dev->graphs = !(ev && ev[0] == '0');
+  ev = getenv("WGPT_BLOCK_GEMV");
+  dev->block_gemv = !(ev && ev[0] == '0');
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&dev->d_err, sizeof(int));
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream);
@@ -289,7 +292,7 @@ static bool gemv_nk_fits(const wgpt_device *dev, int M, int K) {
 
 template <int M, int WK, int CPW>
 static int32_t launch_gemv_nk_t(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
-                                const float *Wt, int K, int N, const Epilogue &epi) {
+                                const float *Wt, int K, int N, const Epilogue &epi, const GreedyPick &gp) {
   constexpr int WC = 8 / WK;
   size_t smem = (size_t)M * K * 4 + (size_t)8 * CPW * M * 4;
   auto kern = gemv_nk_kernel<M, WK, CPW>;
@@ -298,36 +301,84 @@ static int32_t launch_gemv_nk_t(wgpt_device *dev, const float *x, size_t ldx, co
   // Weight slices are pulled towards L2 ahead of the dependency wait unless the matrix would flush L2 (the
   // de-embedding table is larger than L2 and is long enough to be bandwidth-bound on its own).
   int prefetch = (size_t)N * K * 4 <= (size_t(32) << 20) ? 1 : 0;
-  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi, prefetch);
+  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi, prefetch, gp);
   return WGPT_OK;
 }
 
 template <int M>
 static int32_t launch_gemv_nk_m(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
-                                const float *Wt, int K, int N, const Epilogue &epi) {
+                                const float *Wt, int K, int N, const Epilogue &epi, const GreedyPick &gp) {
   // Enough warps to cover the machine several times over: split K across the warps of a CTA when N is small.
   int wk = 1;
   while (wk < 8 && (long long)N * wk < 3000 && K / (wk * 2) >= 256) wk *= 2;
-  if (N >= 16384) return launch_gemv_nk_t<M, 1, 4>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+  if (N >= 16384) return launch_gemv_nk_t<M, 1, 4>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
   switch (wk) {
-    case 1: return launch_gemv_nk_t<M, 1, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 2: return launch_gemv_nk_t<M, 2, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 4: return launch_gemv_nk_t<M, 4, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    default: return launch_gemv_nk_t<M, 8, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 1: return launch_gemv_nk_t<M, 1, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 2: return launch_gemv_nk_t<M, 2, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 4: return launch_gemv_nk_t<M, 4, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    default: return launch_gemv_nk_t<M, 8, 1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
   }
 }
 
+static GreedyPick no_pick() {
+  GreedyPick gp;
+  memset(&gp, 0, sizeof gp);
+  return gp;
+}
+
+// Plan for gemv_block_kernel: one CTA per SM, each owning `cols` consecutive columns whose weights fit in shared
+// memory together with the input rows. Returns false when the block does not fit (the register-streaming kernel
+// is used instead).
+static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, int *cols, int *wk, size_t *smem) {
+  if (N >= 16384 || K % 4 != 0) return false;
+  int c = (N + dev->sm_count - 1) / dev->sm_count;
+  int w = 1;
+  while (c * w < 16 && (K / 4) / (w * 2) >= 32) w *= 2;
+  size_t red = (size_t)(c * w > 8 ? c * w : 8) * M;
+  size_t bytes = ((size_t)c * K + (size_t)M * K + ((red + 3) & ~size_t(3))) * 4 + 16;
+  if (bytes > dev->smem_optin - 2048) return false;
+  *cols = c;
+  *wk = w;
+  *smem = bytes;
+  return true;
+}
+
+template <int M>
+static int32_t launch_gemv_block_t(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
+                                   const float *Wt, int K, int N, int cols, int wk, size_t smem, const Epilogue &epi) {
+  auto kern = gemv_block_kernel<M>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int grid = (N + cols - 1) / cols;
+  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, cols, wk, epi, dev->d_err);
+  return WGPT_OK;
+}
+
 static int32_t launch_gemv_nk(wgpt_device *dev, int M, const float *x, size_t ldx, const float *gamma,
-                              const float *beta, const float *Wt, int K, int N, const Epilogue &epi) {
+                              const float *beta, const float *Wt, int K, int N, const Epilogue &epi,
+                              const GreedyPick &gp = no_pick()) {
+  int cols = 0, wk = 0;
+  size_t smem = 0;
+  if (gp.pval == nullptr && dev->block_gemv && gemv_block_plan(dev, M, K, N, &cols, &wk, &smem)) {
+    switch (M) {
+      case 1: return launch_gemv_block_t<1>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 2: return launch_gemv_block_t<2>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 3: return launch_gemv_block_t<3>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 4: return launch_gemv_block_t<4>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 5: return launch_gemv_block_t<5>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 6: return launch_gemv_block_t<6>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 7: return launch_gemv_block_t<7>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 8: return launch_gemv_block_t<8>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+    }
+  }
   switch (M) {
-    case 1: return launch_gemv_nk_m<1>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 2: return launch_gemv_nk_m<2>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 3: return launch_gemv_nk_m<3>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 4: return launch_gemv_nk_m<4>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 5: return launch_gemv_nk_m<5>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 6: return launch_gemv_nk_m<6>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 7: return launch_gemv_nk_m<7>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
-    case 8: return launch_gemv_nk_m<8>(dev, x, ldx, gamma, beta, Wt, K, N, epi);
+    case 1: return launch_gemv_nk_m<1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 2: return launch_gemv_nk_m<2>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 3: return launch_gemv_nk_m<3>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 4: return launch_gemv_nk_m<4>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 5: return launch_gemv_nk_m<5>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 6: return launch_gemv_nk_m<6>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 7: return launch_gemv_nk_m<7>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
+    case 8: return launch_gemv_nk_m<8>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
   }
   return fail(WGPT_ERR_SHAPE, "gemv rows %d out of range", M);
 }
@@ -507,6 +558,7 @@ static int32_t check_err_word(wgpt_device *dev, const char *what) {
   CK(cudaStreamSynchronize(dev->stream));
   if (h) {
     CK(cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream));
+    if (h == 2) return fail(WGPT_ERR_TIMEOUT, "%s: a bulk copy into shared memory did not complete in time", what);
     return fail(WGPT_ERR_ARG, "%s: token id out of range", what);
   }
   return WGPT_OK;
@@ -775,6 +827,8 @@ struct wgpt_session {
   float *attn_part;
   unsigned int *attn_cnt;
   uint32_t *ids, *next_ids, *out_ids;
+  float *pick_val;  // [n_seq][vocab] per-CTA arg-max candidates of the fused greedy pick
+  int *pick_idx;
   int *d_pos, *d_step;
   std::vector<uint32_t> prompts;  // host copy, [n_seq][n_prompt]
   int n_prompt, n_generated;
@@ -825,12 +879,14 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 2) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, ((size_t)n_seq * p.n_head + 1) * 4);  // + arg-max done counter
   if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->pick_val, (size_t)n_seq * p.vocab_size * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->pick_idx, (size_t)n_seq * p.vocab_size * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->d_pos, 2 * sizeof(int));
   if (e == cudaSuccess) e = cudaMemsetAsync(s->attn_cnt, 0, ((size_t)n_seq * p.n_head + 1) * 4, m->dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), m->dev->stream);
   if (e != cudaSuccess) {
     cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
-    cudaFree(s->next_ids); cudaFree(s->d_pos);
+    cudaFree(s->next_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
     delete s;
     return fail(e == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "session allocation: %s",
                 cudaGetErrorString(e));
@@ -847,7 +903,7 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   drop_step_graph(s);
   session_free_act(s);
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
-  cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos);
+  cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
   delete s;
   return WGPT_OK;
 }
@@ -868,7 +924,10 @@ WGPT_EXPORT int32_t wgpt_session_length(wgpt_session *s, int32_t *length) {
 
 // One forward pass over n_tok new tokens per sequence whose ids are already in `ids` (device, [n_seq*n_tok]).
 // Leaves the logits of each sequence's newest position in s->logits. Does not advance the position.
-static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok) {
+static int32_t pick_and_advance(wgpt_session *s, int n_tok);
+
+// With pick, the greedy choice of every sequence is also made (next_ids, out_ids) and the position advanced.
+static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pick = false) {
   wgpt_model *m = s->m;
   wgpt_device *dev = m->dev;
   const wgpt_params &p = m->p;
@@ -926,13 +985,21 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok) {
   const float *x_last = s->x + (size_t)(n_tok - 1) * E;
   size_t ld_last = (size_t)n_tok * E;
   Epilogue e = plain_epi(s->logits, p.vocab_size, nullptr);
-  if (gemv_nk_fits(dev, s->n_seq, E)) {
-    TRY(launch_gemv_nk(dev, s->n_seq, x_last, ld_last, m->lnf_g, m->lnf_b, m->wte, E, p.vocab_size, e));
-  } else {
-    TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
-    TRY(launch_gemm_simt(dev, true, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
-  }
   s->last_rows = M;
+  if (gemv_nk_fits(dev, s->n_seq, E)) {
+    GreedyPick gp = no_pick();
+    if (pick) {  // arg-max and position advance ride on the de-embedding kernel
+      gp.pval = s->pick_val; gp.pidx = s->pick_idx; gp.counter = s->attn_cnt + (size_t)s->n_seq * H;
+      gp.next_ids = s->next_ids; gp.out_ids = s->out_ids; gp.out_stride = s->out_cap;
+      gp.pos = s->d_pos; gp.step = s->d_step; gp.n_tok = n_tok;
+    }
+    TRY(launch_gemv_nk(dev, s->n_seq, x_last, ld_last, m->lnf_g, m->lnf_b, m->wte, E, p.vocab_size, e, gp));
+    if (pick) s->len += n_tok;
+    return WGPT_OK;
+  }
+  TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
+  TRY(launch_gemm_simt(dev, true, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
+  if (pick) TRY(pick_and_advance(s, n_tok));
   return WGPT_OK;
 }
 
@@ -1000,22 +1067,19 @@ static int32_t pick_and_advance(wgpt_session *s, int n_tok) {
 static int32_t decode_step(wgpt_session *s) {
   wgpt_device *dev = s->m->dev;
   if (!dev->graphs) {
-    TRY(forward(s, s->next_ids, 1));
-    return pick_and_advance(s, 1);
+    return forward(s, s->next_ids, 1, true);
   }
   if (s->step_graph == nullptr) {
     // The first step runs eagerly (it also sets every kernel's shared-memory attribute); the second is captured.
     if (!s->step_warm) {
       s->step_warm = true;
-      TRY(forward(s, s->next_ids, 1));
-      return pick_and_advance(s, 1);
+      return forward(s, s->next_ids, 1, true);
     }
     uint64_t before = dev->launches;
     int len_before = s->len;
     cudaGraph_t graph = nullptr;
     CK(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed));
-    int32_t rc = forward(s, s->next_ids, 1);
-    if (rc == WGPT_OK) rc = pick_and_advance(s, 1);
+    int32_t rc = forward(s, s->next_ids, 1, true);
     cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
     s->len = len_before;  // capturing enqueued nothing
     s->step_graph_launches = dev->launches - before;
@@ -1088,8 +1152,7 @@ WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
     CK(cudaStreamSynchronize(dev->stream));
     s->ids_dirty = false;
   }
-  TRY(forward(s, s->ids, first));
-  TRY(pick_and_advance(s, first));
+  TRY(forward(s, s->ids, first, true));
   for (int i = 1; i < n_new; i++) {
     if (s->len + 1 <= n_ctx) {
       TRY(decode_step(s));
@@ -1112,8 +1175,7 @@ WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
     s->len = 0;
     CK(cudaMemcpyAsync(s->ids, window.data(), window.size() * 4, cudaMemcpyHostToDevice, dev->stream));
     s->ids_dirty = true;
-    TRY(forward(s, s->ids, n_ctx));
-    TRY(pick_and_advance(s, n_ctx));
+    TRY(forward(s, s->ids, n_ctx, true));
     CK(cudaStreamSynchronize(dev->stream));  // `window` is pageable host memory about to go out of scope
   }
   s->n_generated = n_new;
@@ -1200,3 +1262,24 @@ WGPT_EXPORT int32_t wgpt_matmul_static(wgpt_device *dev, int32_t rows, int32_t c
   // reads it, so nothing left over from an earlier call is ever read and nothing needs clearing.
   return gemv_kn_with_scratch(dev, rows, in, W, shared, cols, ksplit, part, plain_epi(out, cols, bias));
 }
+
+#ifdef WGPT_TRACE
+// Development build only: copies the trace records (pairs of 64-bit words) to the host and clears the buffer.
+WGPT_EXPORT int32_t wgpt_debug_trace_read(wgpt_device *dev, unsigned long long *out_host, uint32_t max_records,
+                                          uint32_t *n_records) {
+  TRY(use(dev));
+  CK(cudaStreamSynchronize(dev->stream));
+  unsigned int n = 0;
+  CK(cudaMemcpyFromSymbol(&n, g_trace_n, sizeof n));
+  if (n > (1u << 16)) n = 1u << 16;
+  if (n > max_records) n = max_records;
+  if (n) CK(cudaMemcpyFromSymbol(out_host, g_trace_buf, (size_t)n * 16));
+  unsigned int zero = 0;
+  CK(cudaMemcpyToSymbol(g_trace_n, &zero, sizeof zero));
+  void *tb = nullptr;
+  CK(cudaGetSymbolAddress(&tb, g_trace_buf));
+  CK(cudaMemset(tb, 0, sizeof(unsigned long long) << 17));
+  *n_records = n;
+  return WGPT_OK;
+}
+#endif

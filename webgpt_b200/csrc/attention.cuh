@@ -27,8 +27,11 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
   const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, n_split = gridDim.z, H = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane / LPP, lig = lane % LPP;
+  TRACE_BEGIN(3);
+  trace(3, 0);
   pdl_launch_dependents();
   pdl_wait();  // q, the cache row of this step and *pos come from earlier kernels
+  trace(3, 1);
   const int L = __ldcg(pos) + 1;
   const int chunk = (L + n_split - 1) / n_split;
   const int beg = split * chunk, end = min(L, beg + chunk);
@@ -76,6 +79,7 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     acc.z = acc.z * c0 + ao.z * c1; acc.w = acc.w * c0 + ao.w * c1;
     m = mn;
   }
+  trace(3, 2);
   __shared__ float sm_m[4], sm_l[4];
   __shared__ __align__(16) float sm_acc[4][HS];
   if (g == 0) {
@@ -110,6 +114,7 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     is_last = (prev == (unsigned int)n_split - 1) ? 1u : 0u;
   }
   __syncthreads();
+  trace(3, 3);
   if (!is_last) return;
   __threadfence();
   if (tid < HS) {
@@ -126,6 +131,7 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     out[(size_t)seq * ldo + h * HS + tid] = a / ll;
   }
   if (tid == 0) counters[seq * H + h] = 0u;
+  trace(3, 4);
 }
 
 // ------------------------------------------------------------------------------------------------

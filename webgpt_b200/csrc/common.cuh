@@ -88,6 +88,37 @@ __device__ __forceinline__ uint4 ldg_stream4u(const uint4 *p) {
   return v;
 }
 
+// Development aid, compiled in only with -DWGPT_TRACE: thread 0 of the first and last CTA of a kernel append
+// (globaltimer, kernel id, phase) records to a device buffer that a debug entry point reads back.
+#ifdef WGPT_TRACE
+__device__ unsigned long long g_trace_buf[1 << 17];
+__device__ unsigned int g_trace_n;
+// One atomic per kernel (at entry, ahead of the dependency wait) reserves 8 record slots; later phases only read
+// the timer and store, so they do not stall the traced thread.
+__device__ __forceinline__ unsigned int trace_begin(int kid) {
+  unsigned int base = 0xffffffffu;
+  if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+    base = atomicAdd(&g_trace_n, 8u);
+    if (base + 8 > (1u << 16)) base = 0xffffffffu;
+  }
+  return base;
+}
+__device__ __forceinline__ void trace_at(unsigned int base, int kid, int phase) {
+  if (base != 0xffffffffu) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_trace_buf[2 * (base + phase)] = t;
+    g_trace_buf[2 * (base + phase) + 1] =
+        ((unsigned long long)kid << 16) | ((unsigned long long)phase << 8) | (blockIdx.x == 0 ? 0u : 1u);
+  }
+}
+#define TRACE_BEGIN(kid) const unsigned int trace_base_ = trace_begin(kid)
+#define trace(kid, phase) trace_at(trace_base_, kid, phase)
+#else
+#define TRACE_BEGIN(kid) ((void)0)
+#define trace(kid, phase) ((void)0)
+#endif
+
 // Activations written by an earlier kernel are read with __ldcg (L2, bypassing L1) in every kernel that can be
 // launched programmatically: such a kernel becomes resident, and has its SM's L1 invalidated, while its
 // predecessor is still running, so a line another CTA of the predecessor pulled into that L1 afterwards (for
@@ -103,6 +134,39 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // Asks the memory system to bring [p, p+bytes) into L2 (p 16-byte aligned, bytes a multiple of 16).
 __device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// ---- bulk asynchronous copy (TMA, untiled form) global -> shared, completion counted on an mbarrier ----
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// dst (shared) and src (global) 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+// Bounded wait for the given phase parity: returns false if the copy has not landed after max_polls polls
+// (each poll may itself block for a hardware-defined short time).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_polls) {
+  uint32_t done = 0;
+  for (uint32_t i = 0; i < max_polls && !done; i++) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+  }
+  return done != 0;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

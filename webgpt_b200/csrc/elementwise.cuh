@@ -83,6 +83,8 @@ __global__ void embed_kernel(const uint32_t *__restrict__ idx, const float *__re
                              int vocab, const int *__restrict__ pos, int *err) {
   int m = blockIdx.x;
   if (m >= rows) return;
+  TRACE_BEGIN(4);
+  trace(4, 0);
   pdl_launch_dependents();
   pdl_wait();  // idx and *pos are written by the previous step's arg-max
   uint32_t id = __ldcg(idx + m);

@@ -23,7 +23,7 @@ template <int M, int VEC>
 __global__ void __launch_bounds__(256)
 int8_gemv_partial_kernel(const float *__restrict__ x, const uint32_t *__restrict__ Bq, int K, int N,
                          float *__restrict__ part) {
-  extern __shared__ __align__(16) float smem[];
+  extern __shared__ __align__(128) float smem[];
   constexpr int CPL = 4 * VEC;  // columns per lane
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ksplit = gridDim.y;

@@ -13,20 +13,40 @@
 namespace wgpt {
 
 // ------------------------------------------------------------------------------------------------
+// Optional tail of gemv_nk_kernel for the de-embedding: greedy pick fused into the producing kernel.
+// Every CTA reduces its columns to one (value, index) candidate per row; the last CTA to finish reduces the
+// candidates (lowest index wins ties, globals.js:66-74 with top_k = 1), writes the next input id and the output
+// list entry, and advances the session's position and step counters. pval == nullptr disables it.
+struct GreedyPick {
+  float *pval;            // [M][gridDim.x] candidates
+  int *pidx;
+  unsigned int *counter;  // zero on entry, left zero
+  uint32_t *next_ids;     // [M]
+  uint32_t *out_ids;      // [M][out_stride] or nullptr
+  int out_stride;
+  int *pos, *step;
+  int n_tok;
+};
+
 // x: [M, K] rows at stride ldx; Wt: [N, K]. CTA = 8 warps = (8/WK) column groups x WK slices of K.
 // Each warp accumulates CPW columns over its K slice for all M rows.
-// Dynamic shared memory: M*K floats (staged, optionally normalised, input rows) + 8*CPW*M partial sums.
+// Order of work: (1) allow the next kernel to launch and put this warp's first weights in flight (weights are
+// written by no kernel, so this may run while the previous kernel is still executing); (2) wait for the previous
+// kernel; (3) all threads stage the M input rows in shared memory, one warp per row applies the LayerNorm
+// (instructions.js:451-550); (4) multiply; (5) fixed-order sum of the K slices, epilogue, optional greedy pick.
+// Dynamic shared memory: M*K floats + 8*CPW*M partial sums.
 template <int M, int WK, int CPW>
 __global__ void __launch_bounds__(256)
 gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
                const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, Epilogue epi,
-               int prefetch) {
-  extern __shared__ __align__(16) float smem[];
+               int prefetch, GreedyPick gp) {
+  extern __shared__ __align__(128) float smem[];
   float *xs = smem;
   float *red = smem + (size_t)M * K;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K4 = K >> 2;
   constexpr int WC = 8 / WK;
+  constexpr int PRE = CPW == 1 ? 8 : (CPW == 2 ? 4 : 2);  // float4 per lane and column in flight before the wait
   const int wc = warp / WK, wk = warp % WK;
   const int col0 = (blockIdx.x * WC + wc) * CPW;
   const int beg = (int)(((long long)K4 * wk) / WK), end = (int)(((long long)K4 * (wk + 1)) / WK);
@@ -36,32 +56,50 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
     int col = col0 + c < N ? col0 + c : N - 1;  // clamp: out-of-range columns read a valid row, never stored
     w4[c] = reinterpret_cast<const float4 *>(Wt + (size_t)col * K);
   }
-  // ---- before the dependency wait: let the next kernel start, and pull this warp's weight slice (which no
-  // kernel writes) towards L2 so that the HBM stream does not stop at the kernel boundary ----
-  pdl_launch_dependents();
-  if (prefetch && lane == 0 && end > beg) {
-#pragma unroll
-    for (int c = 0; c < CPW; c++) prefetch_l2(w4[c] + beg, (uint32_t)(end - beg) * 16u);
-  }
-  pdl_wait();
 
-  // ---- stage the input rows; one warp per row does the LayerNorm (instructions.js:451-550) ----
-  for (int m = warp; m < M; m += 8) {
-    const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)m * ldx);
-    float4 *dst = reinterpret_cast<float4 *>(xs + (size_t)m * K);
-    if (gamma == nullptr) {
-      for (int i = lane; i < K4; i += 32) dst[i] = __ldcg(src + i);
-    } else {
+  // (1)
+  TRACE_BEGIN(1);
+  trace(1, 0);
+  pdl_launch_dependents();
+  float4 wpre[CPW][PRE];
+#pragma unroll
+  for (int j = 0; j < PRE; j++) {
+    const int i = beg + lane + 32 * j;
+#pragma unroll
+    for (int c = 0; c < CPW; c++)
+      wpre[c][j] = i < end ? ldg_stream4(w4[c] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (prefetch && lane == 0 && end > beg + 32 * PRE) {
+#pragma unroll
+    for (int c = 0; c < CPW; c++) prefetch_l2(w4[c] + beg + 32 * PRE, (uint32_t)(end - beg - 32 * PRE) * 16u);
+  }
+  // (2)
+  pdl_wait();
+  trace(1, 1);
+
+  // (3)
+  {
+    float4 *xs4w = reinterpret_cast<float4 *>(xs);
+    const size_t ldx4 = ldx >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (int idx = tid; idx < M * K4; idx += 256) {
+      int m = idx / K4, i = idx - m * K4;
+      xs4w[idx] = __ldcg(x4 + (size_t)m * ldx4 + i);
+    }
+  }
+  __syncthreads();
+  if (gamma != nullptr) {
+    for (int m = warp; m < M; m += 8) {
+      float4 *row = reinterpret_cast<float4 *>(xs + (size_t)m * K);
       float s = 0.f;
       for (int i = lane; i < K4; i += 32) {
-        float4 v = __ldcg(src + i);
-        dst[i] = v;
+        float4 v = row[i];
         s += (v.x + v.y) + (v.z + v.w);
       }
       float mean = warp_sum(s) / (float)K;
       float q = 0.f;
       for (int i = lane; i < K4; i += 32) {
-        float4 v = dst[i];
+        float4 v = row[i];
         float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
         q += (a * a + b * b) + (c * c + d * d);
       }
@@ -69,24 +107,36 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
       const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
       const float4 *b4 = reinterpret_cast<const float4 *>(beta);
       for (int i = lane; i < K4; i += 32) {
-        float4 v = dst[i], g = g4[i], b = b4[i];
-        dst[i] = make_float4(g.x * ((v.x - mean) / sd) + b.x, g.y * ((v.y - mean) / sd) + b.y,
+        float4 v = row[i], g = g4[i], b = b4[i];
+        row[i] = make_float4(g.x * ((v.x - mean) / sd) + b.x, g.y * ((v.y - mean) / sd) + b.y,
                              g.z * ((v.z - mean) / sd) + b.z, g.w * ((v.w - mean) / sd) + b.w);
       }
     }
+    __syncthreads();
   }
-  __syncthreads();
 
-  // ---- stream the weight rows ----
+  trace(1, 2);
+  // (4)
   float acc[CPW][M];
 #pragma unroll
   for (int c = 0; c < CPW; c++)
 #pragma unroll
     for (int m = 0; m < M; m++) acc[c][m] = 0.f;
-
   const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
+#pragma unroll
+  for (int j = 0; j < PRE; j++) {
+    const int i = beg + lane + 32 * j;
+    if (i < end) {
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float4 xv = xs4[(size_t)m * K4 + i];
+#pragma unroll
+        for (int c = 0; c < CPW; c++) acc[c][m] += dot4(wpre[c][j], xv);
+      }
+    }
+  }
 #pragma unroll 4
-  for (int i = beg + lane; i < end; i += 32) {
+  for (int i = beg + lane + 32 * PRE; i < end; i += 32) {
     float4 w[CPW];
 #pragma unroll
     for (int c = 0; c < CPW; c++) w[c] = ldg_stream4(w4[c] + i);
@@ -105,7 +155,9 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
       if (lane == 0) red[((wc * WK + wk) * CPW + c) * M + m] = v;
     }
   __syncthreads();
-  // ---- sum the K slices in a fixed order, apply the epilogue ----
+  // (5) sum the K slices in a fixed order, apply the epilogue
+  float outv = -INFINITY;
+  int outn = 0x7fffffff;
   if (tid < WC * CPW * M) {
     int m = tid % M, c = (tid / M) % CPW, g = tid / (M * CPW);
     int n = (blockIdx.x * WC + g) * CPW + c;
@@ -113,9 +165,277 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
       float v = 0.f;
 #pragma unroll
       for (int k = 0; k < WK; k++) v += red[((g * WK + k) * CPW + c) * M + m];
-      epi_store(epi, v, m, n);
+      v = epi_apply(epi, v, m, n);
+      *epi_addr(epi, m, n) = v;
+      outv = v;
+      outn = n;
     }
   }
+  trace(1, 3);
+  if (gp.pval == nullptr) return;
+
+  // ---- greedy pick ----
+  constexpr int NC = WC * CPW * M < 8 ? 8 : WC * CPW * M;  // also holds one candidate per warp in the final reduction
+  __shared__ float cand_v[NC];
+  __shared__ int cand_n[NC];
+  __shared__ unsigned int is_last;
+  if (tid < WC * CPW * M) { cand_v[tid] = outv; cand_n[tid] = outn; }
+  __syncthreads();
+  if (tid < M) {  // candidates of row m sit at tid + M*j; columns ascend with j, so ">" keeps the lowest index
+    float bv = -INFINITY;
+    int bn = 0x7fffffff;
+    for (int j = 0; j < WC * CPW; j++) {
+      float v = cand_v[tid + M * j];
+      int n = cand_n[tid + M * j];
+      if (v > bv || (v == bv && n < bn)) { bv = v; bn = n; }
+    }
+    gp.pval[(size_t)tid * gridDim.x + blockIdx.x] = bv;
+    gp.pidx[(size_t)tid * gridDim.x + blockIdx.x] = bn;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = (atomicAdd(gp.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int my_step = __ldcg(gp.step);
+  for (int m = 0; m < M; m++) {
+    float bv = -INFINITY;
+    int bn = 0x7fffffff;
+    for (int j = tid; j < (int)gridDim.x; j += 256) {
+      float v = __ldcg(gp.pval + (size_t)m * gridDim.x + j);
+      int n = __ldcg(gp.pidx + (size_t)m * gridDim.x + j);
+      if (v > bv || (v == bv && n < bn)) { bv = v; bn = n; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int on = __shfl_xor_sync(0xffffffffu, bn, o);
+      if (ov > bv || (ov == bv && on < bn)) { bv = ov; bn = on; }
+    }
+    __syncthreads();  // cand_* reuse
+    if (lane == 0) { cand_v[warp] = bv; cand_n[warp] = bn; }
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < 8; w++)
+        if (cand_v[w] > bv || (cand_v[w] == bv && cand_n[w] < bn)) { bv = cand_v[w]; bn = cand_n[w]; }
+      if (bn == 0x7fffffff) bn = 0;  // a row of NaNs compares false everywhere: report index 0
+      gp.next_ids[m] = (uint32_t)bn;
+      if (gp.out_ids) gp.out_ids[(size_t)m * gp.out_stride + my_step] = (uint32_t)bn;
+    }
+  }
+  if (tid == 0) {
+    *gp.pos = __ldcg(gp.pos) + gp.n_tok;
+    *gp.step = my_step + 1;
+    *gp.counter = 0u;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// LayerNorm of M rows of K floats held in shared memory, by all 256 threads of the CTA
+// (normStats + norm, instructions.js:451-550). scratch: 8*M floats. Ends with a __syncthreads().
+// gamma and beta are weights: the caller loads element tid of each before waiting on the previous kernel, so
+// their memory latency is off the critical path.
+template <int M>
+__device__ __forceinline__ void cta_layernorm_rows(float *xs, int K, const float *__restrict__ gamma,
+                                                   const float *__restrict__ beta, float *scratch, float4 g_first,
+                                                   float4 b_first) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K4 = K >> 2;
+  float4 *x4 = reinterpret_cast<float4 *>(xs);
+  float part[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float s = 0.f;
+    for (int i = tid; i < K4; i += 256) {
+      float4 v = x4[(size_t)m * K4 + i];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    part[m] = warp_sum(s);
+  }
+  if (lane == 0)
+#pragma unroll
+    for (int m = 0; m < M; m++) scratch[warp * M + m] = part[m];
+  __syncthreads();
+  float mean[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) s += scratch[w * M + m];
+    mean[m] = s / (float)K;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float q = 0.f;
+    for (int i = tid; i < K4; i += 256) {
+      float4 v = x4[(size_t)m * K4 + i];
+      float a = v.x - mean[m], b = v.y - mean[m], c = v.z - mean[m], d = v.w - mean[m];
+      q += (a * a + b * b) + (c * c + d * d);
+    }
+    part[m] = warp_sum(q);
+  }
+  if (lane == 0)
+#pragma unroll
+    for (int m = 0; m < M; m++) scratch[warp * M + m] = part[m];
+  __syncthreads();
+  const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
+  const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float q = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) q += scratch[w * M + m];
+    const float sd = sqrtf(q / (float)K + 1e-5f);
+    for (int i = tid; i < K4; i += 256) {
+      // g_first / b_first hold gamma and beta of element tid, fetched by the caller ahead of its dependency wait
+      float4 v = x4[(size_t)m * K4 + i], g = i == tid ? g_first : g4[i], b = i == tid ? b_first : b4[i];
+      x4[(size_t)m * K4 + i] = make_float4(g.x * ((v.x - mean[m]) / sd) + b.x, g.y * ((v.y - mean[m]) / sd) + b.y,
+                                           g.z * ((v.z - mean[m]) / sd) + b.z, g.w * ((v.w - mean[m]) / sd) + b.w);
+    }
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------------
+// The layer GEMVs of a decode step (N up to a few thousand columns, 2-10 MB of weights): one CTA per SM owns
+// `cols` consecutive output columns, i.e. one contiguous block of Wt, and fetches the whole block into shared
+// memory with bulk asynchronous copies issued before the dependency wait, so the HBM stream of this kernel runs
+// while the previous kernel is still executing. After the wait: stage + normalise the input rows, wait for the
+// copies (bounded), multiply out of shared memory. Work items are (column, K slice), wk in {1,2,4,8}; a warp
+// keeps the same K slice for all its items and handles three columns at a time; the K slices of a column are
+// summed in a fixed order.
+// Dynamic shared memory: [cols*K] weights, [M*K] input rows, [max(cols*wk, 8)*M] partial sums, one mbarrier.
+// *err is set (and nothing stored) if the copies do not land within the poll limit.
+template <int M>
+__global__ void __launch_bounds__(256)
+gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
+                  const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, int cols, int wk,
+                  Epilogue epi, int *err) {
+  extern __shared__ __align__(128) float smem[];
+  float *wbuf = smem;
+  float *xs = wbuf + (size_t)cols * K;
+  float *red = xs + (size_t)M * K;
+  const int red_floats = (max(cols * wk, 8) * M + 3) & ~3;
+  uint64_t *bar = reinterpret_cast<uint64_t *>(red + red_floats);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K4 = K >> 2;
+  const int col0 = blockIdx.x * cols;
+  const int ncol = min(cols, N - col0);
+
+  TRACE_BEGIN(2);
+  trace(2, 0);
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    const uint32_t row_bytes = (uint32_t)K * 4u;
+    mbar_expect_tx(bar, row_bytes * (uint32_t)ncol);
+    // a few rows per copy keeps each request modest and lets several be in flight
+    const int rows_per_copy = max(1, (int)(16384u / row_bytes));
+    for (int r = 0; r < ncol; r += rows_per_copy) {
+      int nr = min(rows_per_copy, ncol - r);
+      bulk_g2s(wbuf + (size_t)r * K, Wt + (size_t)(col0 + r) * K, row_bytes * (uint32_t)nr, bar);
+    }
+  }
+  // The output this thread will finish in the epilogue: fetch its bias now (a weight: readable before the wait).
+  const bool has_out = tid < ncol * M;
+  const int oc = has_out ? tid / M : 0, om = has_out ? tid - oc * M : 0;
+  float bias_v = 0.f, scale_v = 1.f;
+  if (has_out && epi.bias) bias_v = epi.bias[col0 + oc];
+  if (has_out && epi.colscale) scale_v = epi.colscale[col0 + oc];
+  float4 g_first = make_float4(0.f, 0.f, 0.f, 0.f), b_first = g_first;
+  if (gamma != nullptr && tid < K4) {
+    g_first = reinterpret_cast<const float4 *>(gamma)[tid];
+    b_first = reinterpret_cast<const float4 *>(beta)[tid];
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  trace(2, 1);
+  float res_v = 0.f;
+  if (has_out && epi.residual) res_v = __ldcg(epi.residual + (size_t)om * epi.ld + col0 + oc);
+  {
+    float4 *xs4w = reinterpret_cast<float4 *>(xs);
+    const size_t ldx4 = ldx >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (int idx = tid; idx < M * K4; idx += 256) {
+      int m = idx / K4, i = idx - m * K4;
+      xs4w[idx] = __ldcg(x4 + (size_t)m * ldx4 + i);
+    }
+  }
+  __syncthreads();  // also makes the mbarrier initialisation visible to every thread
+  trace(2, 2);
+  if (gamma != nullptr) cta_layernorm_rows<M>(xs, K, gamma, beta, red, g_first, b_first);
+
+  // Bounded wait for the weights. On expiry: flag the error, give the copies one more bounded chance to land
+  // (shared memory must not be released under them), and leave without storing.
+  trace(2, 3);
+  const int landed = __syncthreads_and(mbar_wait(bar, 0, 1u << 20) ? 1 : 0);  // one decision for the whole CTA
+  if (!landed) {
+    if (tid == 0) atomicExch(err, 2);
+    mbar_wait(bar, 0, 1u << 22);
+    return;
+  }
+
+  trace(2, 4);
+  const float4 *w4 = reinterpret_cast<const float4 *>(wbuf);
+  const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
+  const int items = ncol * wk;
+  const int ks = warp % wk;  // 8 % wk == 0: every item of this warp has the same K slice
+  const int beg = (int)(((long long)K4 * ks) / wk), end = (int)(((long long)K4 * (ks + 1)) / wk);
+  constexpr int NB = 3;
+  for (int it0 = warp; it0 < items; it0 += 8 * NB) {
+    int c[NB];
+    bool valid[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      int it = it0 + 8 * b;
+      valid[b] = it < items;
+      c[b] = valid[b] ? it / wk : 0;
+    }
+    float acc[NB][M];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[b][m] = 0.f;
+#pragma unroll 2
+    for (int i = beg + lane; i < end; i += 32) {
+      float4 xv[M];
+#pragma unroll
+      for (int m = 0; m < M; m++) xv[m] = xs4[(size_t)m * K4 + i];
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+        if (valid[b]) {
+          float4 w = w4[(size_t)c[b] * K4 + i];
+#pragma unroll
+          for (int m = 0; m < M; m++) acc[b][m] += dot4(w, xv[m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float v = warp_sum(acc[b][m]);
+        if (lane == 0 && valid[b]) red[(c[b] * wk + ks) * M + m] = v;
+      }
+  }
+  trace(2, 5);
+  __syncthreads();
+  if (has_out) {  // first 256 outputs: bias / residual were fetched ahead
+    float v = 0.f;
+    for (int k = 0; k < wk; k++) v += red[(oc * wk + k) * M + om];
+    v = v * scale_v + bias_v;
+    if (epi.act == 1) v = gelu_f(v);
+    if (epi.residual) v += res_v;
+    *epi_addr(epi, om, col0 + oc) = v;
+  }
+  for (int o = tid + 256; o < ncol * M; o += 256) {
+    const int cc = o / M, m = o - cc * M;
+    float v = 0.f;
+    for (int k = 0; k < wk; k++) v += red[(cc * wk + k) * M + m];
+    epi_store(epi, v, m, col0 + cc);
+  }
+  trace(2, 6);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -126,7 +446,7 @@ template <int M>
 __global__ void __launch_bounds__(256)
 gemv_kn_partial_kernel(const float *__restrict__ x, const float *__restrict__ W, int K, int N,
                        float *__restrict__ part) {
-  extern __shared__ __align__(16) float smem[];  // xs[M][kslice] + red[8][M][128]
+  extern __shared__ __align__(128) float smem[];  // xs[M][kslice] + red[8][M][128]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ksplit = gridDim.y;
   const int kbeg = (int)(((long long)(K / 4) * blockIdx.y) / ksplit) * 4;
