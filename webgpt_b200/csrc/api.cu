@@ -81,25 +81,36 @@ struct wgpt_device {
 // Launch for kernels that call pdl_wait() before touching anything an earlier kernel wrote: with dev->pdl they
 // carry the programmatic-serialisation attribute and may start while their predecessor is still running.
 template <typename... KArgs, typename... Args>
-static cudaError_t launch_ex(bool pdl, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                             Args... args) {
+static cudaError_t launch_ex(bool pdl, int cluster_z, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid,
+                             dim3 block, size_t smem, Args... args) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  if (cluster_z > 1) {  // thread-block clusters along z
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = (unsigned)cluster_z;
+    n++;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 #define LAUNCH_PDL(dev, kernel, grid, block, smem, ...)                                          \
   do {                                                                                           \
-    CK(launch_ex((dev)->pdl, (dev)->stream, kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__)); \
+    CK(launch_ex((dev)->pdl, 0, (dev)->stream, kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__)); \
     (dev)->launches++;                                                                           \
   } while (0)
 
@@ -329,13 +340,14 @@ static GreedyPick no_pick() {
 // Plan for gemv_block_kernel: one CTA per SM, each owning `cols` consecutive columns whose weights fit in shared
 // memory together with the input rows. Returns false when the block does not fit (the register-streaming kernel
 // is used instead).
-static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, int *cols, int *wk, size_t *smem) {
+static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, bool layernorm, int *cols, int *wk,
+                            size_t *smem) {
   if (N >= 16384 || K % 4 != 0) return false;
   int c = (N + dev->sm_count - 1) / dev->sm_count;
   int w = 1;
   while (c * w < 16 && (K / 4) / (w * 2) >= 32) w *= 2;
   size_t red = (size_t)(c * w > 8 ? c * w : 8) * M;
-  size_t bytes = ((size_t)c * K + (size_t)M * K + ((red + 3) & ~size_t(3))) * 4 + 16;
+  size_t bytes = ((size_t)c * K + (size_t)M * K * (layernorm ? 2 : 1) + ((red + 3) & ~size_t(3))) * 4 + 16;
   if (bytes > dev->smem_optin - 2048) return false;
   *cols = c;
   *wk = w;
@@ -345,30 +357,38 @@ static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, int *co
 
 template <int M>
 static int32_t launch_gemv_block_t(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
-                                   const float *Wt, int K, int N, int cols, int wk, size_t smem, const Epilogue &epi) {
+                                   const float *Wt, int K, int N, int cols, int wk, size_t smem, const Epilogue &epi,
+                                   const AttnPartials &ap) {
   auto kern = gemv_block_kernel<M>;
   if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = (N + cols - 1) / cols;
-  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, cols, wk, epi, dev->d_err);
+  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, cols, wk, epi, dev->d_err, ap);
   return WGPT_OK;
 }
 
 static int32_t launch_gemv_nk(wgpt_device *dev, int M, const float *x, size_t ldx, const float *gamma,
                               const float *beta, const float *Wt, int K, int N, const Epilogue &epi,
-                              const GreedyPick &gp = no_pick()) {
+                              const GreedyPick &gp = no_pick(), const AttnPartials *partials = nullptr) {
+  AttnPartials ap;
+  memset(&ap, 0, sizeof ap);
+  if (partials) ap = *partials;
   int cols = 0, wk = 0;
   size_t smem = 0;
-  if (gp.pval == nullptr && dev->block_gemv && gemv_block_plan(dev, M, K, N, &cols, &wk, &smem)) {
+  if (gp.pval == nullptr && dev->block_gemv && gemv_block_plan(dev, M, K, N, gamma != nullptr, &cols, &wk, &smem)) {
     switch (M) {
-      case 1: return launch_gemv_block_t<1>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 2: return launch_gemv_block_t<2>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 3: return launch_gemv_block_t<3>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 4: return launch_gemv_block_t<4>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 5: return launch_gemv_block_t<5>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 6: return launch_gemv_block_t<6>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 7: return launch_gemv_block_t<7>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
-      case 8: return launch_gemv_block_t<8>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi);
+      case 1: return launch_gemv_block_t<1>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 2: return launch_gemv_block_t<2>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 3: return launch_gemv_block_t<3>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 4: return launch_gemv_block_t<4>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 5: return launch_gemv_block_t<5>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 6: return launch_gemv_block_t<6>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 7: return launch_gemv_block_t<7>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
+      case 8: return launch_gemv_block_t<8>(dev, x, ldx, gamma, beta, Wt, K, N, cols, wk, smem, epi, ap);
     }
+  }
+  if (ap.part != nullptr) {  // the register-streaming kernel reads merged rows: merge into x first
+    dim3 mg((ap.H * ap.hs / 4 + 127) / 128, M);
+    LAUNCH_PDL(dev, attn_merge_kernel, mg, 128, 0, ap, const_cast<float *>(x), (int)ldx);
   }
   switch (M) {
     case 1: return launch_gemv_nk_m<1>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
@@ -475,12 +495,12 @@ static int32_t launch_attn_prefill(wgpt_device *dev, int hs, const float *q, int
 
 static int32_t launch_attn_decode(wgpt_device *dev, int hs, const float *q, int ldq, const float *kc, const float *vc,
                                   int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_seq, int H, int n_split,
-                                  const int *pos, float scale, float *part, unsigned int *counters) {
+                                  const int *pos, float scale, float *part) {
   dim3 grid(H, n_seq, n_split);
-#define CASE(HSV)                                                                                             \
-  case HSV:                                                                                                   \
-    LAUNCH_PDL(dev, attn_decode_kernel<HSV>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
-               part, counters);                                                                                   \
+#define CASE(HSV)                                                                                                   \
+  case HSV:                                                                                                         \
+    LAUNCH_PDL(dev, attn_decode_kernel<HSV>, grid, 256, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
+               part);                                                                                               \
     return WGPT_OK;
   switch (hs) {
     CASE(4) CASE(8) CASE(16) CASE(32) CASE(64) CASE(128)
@@ -824,7 +844,7 @@ struct wgpt_session {
   int n_split;
   float *x, *h, *q, *o, *f, *logits;
   float *kc, *vc;  // [n_layer][n_seq][n_ctx][E]
-  float *attn_part;
+  float *attn_part;  // decode-attention partials, [n_seq][n_head][n_split][hs + 4]
   unsigned int *attn_cnt;
   uint32_t *ids, *next_ids, *out_ids;
   float *pick_val;  // [n_seq][vocab] per-CTA arg-max candidates of the fused greedy pick
@@ -871,12 +891,14 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   s->n_seq = n_seq;
   const wgpt_params &p = m->p;
   size_t kv = (size_t)p.n_layer * n_seq * p.n_ctx * p.n_embd;
-  int split = (2 * m->dev->sm_count) / (p.n_head * n_seq);
-  s->n_split = split < 1 ? 1 : (split > 16 ? 16 : split);
+  // position slices per (sequence, head): a cluster of 1, 2, 4 or 8 CTAs, enough to put about two CTAs on every SM
+  int split = 1;
+  while (split < 8 && p.n_head * n_seq * split * 2 <= 2 * m->dev->sm_count) split *= 2;
+  s->n_split = split;
   cudaError_t e = cudaMalloc(&s->kc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->vc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->logits, (size_t)n_seq * p.vocab_size * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 2) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 4) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, ((size_t)n_seq * p.n_head + 1) * 4);  // + arg-max done counter
   if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_val, (size_t)n_seq * p.vocab_size * 4);
@@ -960,14 +982,27 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     }
     if (n_tok == 1)
       TRY(launch_attn_decode(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, s->n_seq, H, s->n_split, s->d_pos,
-                             m->scale, s->attn_part, s->attn_cnt));
+                             m->scale, s->attn_part));
     else
       TRY(launch_attn_prefill(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, n_tok, s->n_seq, H, s->d_pos,
                               m->scale));
     {  // attention output projection + residual
       Epilogue e = plain_epi(s->x, E, L.bo);
       e.residual = s->x;
-      TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+      if (n_tok == 1 && s->n_split > 1) {
+        // the decode attention left per-slice partials; the projection merges them while staging its input
+        AttnPartials ap;
+        ap.part = s->attn_part; ap.n_split = s->n_split; ap.H = H; ap.hs = hs;
+        if (gemv_nk_fits(dev, M, E)) {
+          TRY(launch_gemv_nk(dev, M, s->o, (size_t)E, nullptr, nullptr, L.wo_t, E, E, e, no_pick(), &ap));
+        } else {
+          dim3 mg((E / 4 + 127) / 128, M);
+          LAUNCH_PDL(dev, attn_merge_kernel, mg, 128, 0, ap, s->o, E);
+          TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+        }
+      } else {
+        TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+      }
     }
     {  // LN2 + MLP up-projection + GELU
       Epilogue e = plain_epi(s->f, F, L.bfc);

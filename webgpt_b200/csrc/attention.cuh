@@ -11,41 +11,52 @@
 namespace wgpt {
 
 // ------------------------------------------------------------------------------------------------
-// Decode: one query row per sequence at position *pos (keys 0..*pos). grid = (H, n_seq, n_split);
-// each CTA (4 warps) handles a slice of the positions with an online softmax, writes an un-normalised
-// partial (max, sum, acc[HS]) to scratch, and the last CTA to finish for a (seq, head) merges the
-// slices in slice order. HBM-bound: reads 2*HS*4 bytes per position per head.
-// scratch: part[(seq*H + h)*n_split + s][HS + 2] floats, counters[seq*H + h] (zero before first use;
-// the merging CTA re-zeroes its counter).
+// Decode: one query row per sequence at position *pos (keys 0..*pos). grid = (H, n_seq, n_split): the CTAs along
+// z share one (sequence, head) and each takes a slice of the positions. A CTA (8 warps) runs an online softmax
+// over its slice. With n_split == 1 it writes the head's output; otherwise it writes an un-normalised partial
+// (acc[HS], max, sum, 2 pad) to scratch, part[((seq*H + h)*n_split + split)*(HS+4)], and the consumer merges the
+// slices in slice order while it stages its input (attn_merged_value below): no atomics, no extra pass.
+// HBM-bound: reads 2*HS*4 bytes per position per head. Before the dependency wait the CTA asks for its slice of
+// the cache in L2, computed from the position counter as it stands then (possibly one step old: the rows of
+// earlier positions never change, so a stale bound only misses the newest row).
 template <int HS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc, const float *__restrict__ vc,
                    int ldkv, size_t kv_seq_stride, float *__restrict__ out, int ldo, const int *__restrict__ pos,
-                   float scale, float *__restrict__ part, unsigned int *__restrict__ counters) {
+                   float scale, float *__restrict__ part) {
   constexpr int LPP = HS / 4;      // lanes per position (one float4 each)
   constexpr int G = 32 / LPP;      // positions per warp iteration
+  constexpr int NW = 8;
   const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, n_split = gridDim.z, H = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane / LPP, lig = lane % LPP;
+  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
   TRACE_BEGIN(3);
   trace(3, 0);
   pdl_launch_dependents();
+  {
+    const int Ls = __ldcg(pos) + 1;
+    const int chunk_s = (Ls + n_split - 1) / n_split;
+    const int beg_s = split * chunk_s, end_s = min(Ls, beg_s + chunk_s);
+    for (int r = beg_s + (tid >> 1); r < end_s; r += 128)
+      prefetch_l2(((tid & 1) ? vb : kb) + (size_t)r * ldkv, HS * 4);
+  }
   pdl_wait();  // q, the cache row of this step and *pos come from earlier kernels
   trace(3, 1);
   const int L = __ldcg(pos) + 1;
   const int chunk = (L + n_split - 1) / n_split;
   const int beg = split * chunk, end = min(L, beg + chunk);
-
   const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4));
-  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
-  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS + lig * 4;
+  kb += lig * 4;
+  vb += lig * 4;
 
   float m = -INFINITY, l = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   // The trip count is the same for every lane of the warp (the shuffles below name all 32 lanes); a group whose
   // position falls past the end of the slice runs the iteration with `valid` false and contributes nothing.
 #pragma unroll 2
-  for (int j0 = beg + warp * G; j0 < end; j0 += 4 * G) {
+  for (int j0 = beg + warp * G; j0 < end; j0 += NW * G) {
     const int j = j0 + g;
     const bool valid = j < end;
     const int jj = valid ? j : end - 1;  // in-bounds address for the idle group
@@ -80,58 +91,82 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     m = mn;
   }
   trace(3, 2);
-  __shared__ float sm_m[4], sm_l[4];
-  __shared__ __align__(16) float sm_acc[4][HS];
+  __shared__ float sm_m[NW], sm_l[NW];
+  __shared__ __align__(16) float sm_acc[NW][HS];
   if (g == 0) {
     *reinterpret_cast<float4 *>(&sm_acc[warp][lig * 4]) = acc;
     if (lig == 0) { sm_m[warp] = m; sm_l[warp] = l; }
   }
   __syncthreads();
-  float *my = part + ((size_t)(seq * H + h) * n_split + split) * (HS + 2);
   if (tid < HS) {
-    float mm = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float mm = sm_m[0];
+#pragma unroll
+    for (int w = 1; w < NW; w++) mm = fmaxf(mm, sm_m[w]);
     float ll = 0.f, a = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
+    for (int w = 0; w < NW; w++) {
       float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - mm);
       ll += sm_l[w] * c;
       a += sm_acc[w][tid] * c;
     }
     if (n_split == 1) {
       out[(size_t)seq * ldo + h * HS + tid] = a / ll;
-      return;
+    } else {
+      float *my = part + ((size_t)(seq * H + h) * n_split + split) * (HS + 4);
+      my[tid] = a;
+      if (tid == 0) { my[HS] = mm; my[HS + 1] = ll; }
     }
-    my[2 + tid] = a;
-    if (tid == 0) { my[0] = mm; my[1] = ll; }
   }
-  if (n_split == 1) return;
-  // ---- last CTA of this (seq, head) merges the slices ----
-  __shared__ unsigned int is_last;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    unsigned int prev = atomicAdd(&counters[seq * H + h], 1u);
-    is_last = (prev == (unsigned int)n_split - 1) ? 1u : 0u;
-  }
-  __syncthreads();
-  trace(3, 3);
-  if (!is_last) return;
-  __threadfence();
-  if (tid < HS) {
-    const float *p0 = part + (size_t)(seq * H + h) * n_split * (HS + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < n_split; s++) mm = fmaxf(mm, __ldcg(p0 + (size_t)s * (HS + 2)));
-    float ll = 0.f, a = 0.f;
-    for (int s = 0; s < n_split; s++) {
-      float ms = __ldcg(p0 + (size_t)s * (HS + 2));
-      float c = (ms == -INFINITY) ? 0.f : expf(ms - mm);
-      ll += __ldcg(p0 + (size_t)s * (HS + 2) + 1) * c;
-      a += __ldcg(p0 + (size_t)s * (HS + 2) + 2 + tid) * c;
-    }
-    out[(size_t)seq * ldo + h * HS + tid] = a / ll;
-  }
-  if (tid == 0) counters[seq * H + h] = 0u;
   trace(3, 4);
+}
+
+// Description of attention partials left by attn_decode_kernel with n_split > 1, for consumers that merge them
+// while staging their input. part == nullptr: no merge, the input is read as is.
+struct AttnPartials {
+  const float *part;
+  int n_split, H, hs;
+};
+
+// Elements c..c+3 (c % 4 == 0, all in one head) of the attention output of sequence `seq`: the slices'
+// partials combined in slice order.
+__device__ __forceinline__ float4 attn_merged_value4(const AttnPartials &ap, int seq, int c) {
+  const int h = c / ap.hs, d = c - h * ap.hs;
+  const int stride = ap.hs + 4;
+  const float *p0 = ap.part + (size_t)(seq * ap.H + h) * ap.n_split * stride;
+  float pm[8], pl[8];
+  float4 pa[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    if (r < ap.n_split) {
+      const float *pr = p0 + (size_t)r * stride;
+      pa[r] = __ldcg(reinterpret_cast<const float4 *>(pr + d));
+      float2 ml = __ldcg(reinterpret_cast<const float2 *>(pr + ap.hs));
+      pm[r] = ml.x;
+      pl[r] = ml.y;
+    } else {
+      pm[r] = -INFINITY; pl[r] = 0.f; pa[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  float mm = pm[0];
+#pragma unroll
+  for (int r = 1; r < 8; r++) mm = fmaxf(mm, pm[r]);
+  float ll = 0.f;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    float c2 = (pm[r] == -INFINITY) ? 0.f : expf(pm[r] - mm);
+    ll += pl[r] * c2;
+    a.x += pa[r].x * c2; a.y += pa[r].y * c2; a.z += pa[r].z * c2; a.w += pa[r].w * c2;
+  }
+  return make_float4(a.x / ll, a.y / ll, a.z / ll, a.w / ll);
+}
+
+// Stand-alone merge for consumers that cannot merge on the fly: out[seq, c] for c in [0, H*hs).
+__global__ void attn_merge_kernel(AttnPartials ap, float *__restrict__ out, int ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c < ap.H * ap.hs) *reinterpret_cast<float4 *>(out + (size_t)seq * ldo + c) = attn_merged_value4(ap, seq, c);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -8,6 +8,7 @@
 //  - gemm_simt_kernel: general M; 64x64x16 tiles, 4x4 register tile per thread. The FP32 reference mode for
 //                     the tensor-core path and the executor of the per-operator API.
 #pragma once
+#include "attention.cuh"
 #include "common.cuh"
 
 namespace wgpt {
@@ -232,67 +233,44 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
 }
 
 // ------------------------------------------------------------------------------------------------
-// LayerNorm of M rows of K floats held in shared memory, by all 256 threads of the CTA
-// (normStats + norm, instructions.js:451-550). scratch: 8*M floats. Ends with a __syncthreads().
-// gamma and beta are weights: the caller loads element tid of each before waiting on the previous kernel, so
-// their memory latency is off the critical path.
+// LayerNorm of M rows of K floats held in shared memory (normStats + norm, instructions.js:451-550).
+// Every warp computes the two-pass statistics of every row itself (the row is only K floats, and this needs no
+// block-wide barrier); the 256 threads then share the writes of the normalised rows into a second buffer.
+// Ends with one __syncthreads(). gamma and beta are weights: the caller loads element tid of each before
+// waiting on the previous kernel, so their memory latency is off the critical path.
 template <int M>
-__device__ __forceinline__ void cta_layernorm_rows(float *xs, int K, const float *__restrict__ gamma,
-                                                   const float *__restrict__ beta, float *scratch, float4 g_first,
-                                                   float4 b_first) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ void cta_layernorm_rows(const float *raw, float *normed, int K,
+                                                   const float *__restrict__ gamma, const float *__restrict__ beta,
+                                                   float4 g_first, float4 b_first) {
+  const int tid = threadIdx.x, lane = tid & 31;
   const int K4 = K >> 2;
-  float4 *x4 = reinterpret_cast<float4 *>(xs);
-  float part[M];
-#pragma unroll
-  for (int m = 0; m < M; m++) {
-    float s = 0.f;
-    for (int i = tid; i < K4; i += 256) {
-      float4 v = x4[(size_t)m * K4 + i];
-      s += (v.x + v.y) + (v.z + v.w);
-    }
-    part[m] = warp_sum(s);
-  }
-  if (lane == 0)
-#pragma unroll
-    for (int m = 0; m < M; m++) scratch[warp * M + m] = part[m];
-  __syncthreads();
-  float mean[M];
-#pragma unroll
-  for (int m = 0; m < M; m++) {
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) s += scratch[w * M + m];
-    mean[m] = s / (float)K;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int m = 0; m < M; m++) {
-    float q = 0.f;
-    for (int i = tid; i < K4; i += 256) {
-      float4 v = x4[(size_t)m * K4 + i];
-      float a = v.x - mean[m], b = v.y - mean[m], c = v.z - mean[m], d = v.w - mean[m];
-      q += (a * a + b * b) + (c * c + d * d);
-    }
-    part[m] = warp_sum(q);
-  }
-  if (lane == 0)
-#pragma unroll
-    for (int m = 0; m < M; m++) scratch[warp * M + m] = part[m];
-  __syncthreads();
+  const float4 *x4 = reinterpret_cast<const float4 *>(raw);
+  float4 *o4 = reinterpret_cast<float4 *>(normed);
   const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
   const float4 *b4 = reinterpret_cast<const float4 *>(beta);
 #pragma unroll
   for (int m = 0; m < M; m++) {
+    float s = 0.f;
+#pragma unroll 4
+    for (int i = lane; i < K4; i += 32) {
+      float4 v = x4[(size_t)m * K4 + i];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean = warp_sum(s) / (float)K;
     float q = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) q += scratch[w * M + m];
-    const float sd = sqrtf(q / (float)K + 1e-5f);
+#pragma unroll 4
+    for (int i = lane; i < K4; i += 32) {
+      float4 v = x4[(size_t)m * K4 + i];
+      float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+      q += (a * a + b * b) + (c * c + d * d);
+    }
+    // one division per row; the shader divides every element by sd (instructions.js:544), which differs from
+    // multiplying by 1/sd by at most one unit in the last place
+    const float rsd = 1.0f / sqrtf(warp_sum(q) / (float)K + 1e-5f);
     for (int i = tid; i < K4; i += 256) {
-      // g_first / b_first hold gamma and beta of element tid, fetched by the caller ahead of its dependency wait
       float4 v = x4[(size_t)m * K4 + i], g = i == tid ? g_first : g4[i], b = i == tid ? b_first : b4[i];
-      x4[(size_t)m * K4 + i] = make_float4(g.x * ((v.x - mean[m]) / sd) + b.x, g.y * ((v.y - mean[m]) / sd) + b.y,
-                                           g.z * ((v.z - mean[m]) / sd) + b.z, g.w * ((v.w - mean[m]) / sd) + b.w);
+      o4[(size_t)m * K4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
+                                           g.z * ((v.z - mean) * rsd) + b.z, g.w * ((v.w - mean) * rsd) + b.w);
     }
   }
   __syncthreads();
@@ -306,17 +284,19 @@ __device__ __forceinline__ void cta_layernorm_rows(float *xs, int K, const float
 // copies (bounded), multiply out of shared memory. Work items are (column, K slice), wk in {1,2,4,8}; a warp
 // keeps the same K slice for all its items and handles three columns at a time; the K slices of a column are
 // summed in a fixed order.
-// Dynamic shared memory: [cols*K] weights, [M*K] input rows, [max(cols*wk, 8)*M] partial sums, one mbarrier.
+// Dynamic shared memory: [cols*K] weights, [M*K] input rows (twice with LayerNorm), [max(cols*wk, 8)*M]
+// partial sums, one mbarrier.
 // *err is set (and nothing stored) if the copies do not land within the poll limit.
 template <int M>
 __global__ void __launch_bounds__(256)
 gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
                   const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, int cols, int wk,
-                  Epilogue epi, int *err) {
+                  Epilogue epi, int *err, AttnPartials ap) {
   extern __shared__ __align__(128) float smem[];
   float *wbuf = smem;
-  float *xs = wbuf + (size_t)cols * K;
-  float *red = xs + (size_t)M * K;
+  float *xs = wbuf + (size_t)cols * K;                                    // input rows as staged
+  float *xn = gamma != nullptr ? xs + (size_t)M * K : xs;                // normalised rows (LayerNorm only)
+  float *red = xn + (size_t)M * K;
   const int red_floats = (max(cols * wk, 8) * M + 3) & ~3;
   uint64_t *bar = reinterpret_cast<uint64_t *>(red + red_floats);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -343,6 +323,12 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   float bias_v = 0.f, scale_v = 1.f;
   if (has_out && epi.bias) bias_v = epi.bias[col0 + oc];
   if (has_out && epi.colscale) scale_v = epi.colscale[col0 + oc];
+  // All index arithmetic happens here, ahead of the wait (integer division is slow enough to matter after it).
+  const int wk_log2 = 31 - __clz(wk);          // wk is a power of two
+  const int ks = warp & (wk - 1);              // 8 % wk == 0: every item of this warp has the same K slice
+  const int beg = (int)(((unsigned)K4 * (unsigned)ks) >> wk_log2);
+  const int end = (int)(((unsigned)K4 * (unsigned)(ks + 1)) >> wk_log2);
+  const int items = ncol << wk_log2;
   float4 g_first = make_float4(0.f, 0.f, 0.f, 0.f), b_first = g_first;
   if (gamma != nullptr && tid < K4) {
     g_first = reinterpret_cast<const float4 *>(gamma)[tid];
@@ -357,14 +343,20 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     float4 *xs4w = reinterpret_cast<float4 *>(xs);
     const size_t ldx4 = ldx >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    for (int idx = tid; idx < M * K4; idx += 256) {
-      int m = idx / K4, i = idx - m * K4;
-      xs4w[idx] = __ldcg(x4 + (size_t)m * ldx4 + i);
+    if (ap.part != nullptr) {  // the input rows are attention outputs still split into position slices
+#pragma unroll
+      for (int m = 0; m < M; m++)
+        for (int i = tid; i < K4; i += 256) xs4w[(size_t)m * K4 + i] = attn_merged_value4(ap, m, 4 * i);
+    } else {
+#pragma unroll
+      for (int m = 0; m < M; m++)
+#pragma unroll 4
+        for (int i = tid; i < K4; i += 256) xs4w[(size_t)m * K4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
     }
   }
   __syncthreads();  // also makes the mbarrier initialisation visible to every thread
   trace(2, 2);
-  if (gamma != nullptr) cta_layernorm_rows<M>(xs, K, gamma, beta, red, g_first, b_first);
+  if (gamma != nullptr) cta_layernorm_rows<M>(xs, xn, K, gamma, beta, g_first, b_first);
 
   // Bounded wait for the weights. On expiry: flag the error, give the copies one more bounded chance to land
   // (shared memory must not be released under them), and leave without storing.
@@ -378,10 +370,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
 
   trace(2, 4);
   const float4 *w4 = reinterpret_cast<const float4 *>(wbuf);
-  const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
-  const int items = ncol * wk;
-  const int ks = warp % wk;  // 8 % wk == 0: every item of this warp has the same K slice
-  const int beg = (int)(((long long)K4 * ks) / wk), end = (int)(((long long)K4 * (ks + 1)) / wk);
+  const float4 *xs4 = reinterpret_cast<const float4 *>(xn);
   constexpr int NB = 3;
   for (int it0 = warp; it0 < items; it0 += 8 * NB) {
     int c[NB];
@@ -390,14 +379,14 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     for (int b = 0; b < NB; b++) {
       int it = it0 + 8 * b;
       valid[b] = it < items;
-      c[b] = valid[b] ? it / wk : 0;
+      c[b] = valid[b] ? (it >> wk_log2) : 0;
     }
     float acc[NB][M];
 #pragma unroll
     for (int b = 0; b < NB; b++)
 #pragma unroll
       for (int m = 0; m < M; m++) acc[b][m] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
     for (int i = beg + lane; i < end; i += 32) {
       float4 xv[M];
 #pragma unroll
@@ -411,6 +400,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
         }
       }
     }
+    trace(2, 7);
 #pragma unroll
     for (int b = 0; b < NB; b++)
 #pragma unroll
