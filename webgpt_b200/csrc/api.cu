@@ -344,9 +344,11 @@ static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, bool la
                             size_t *smem) {
   if (N >= 16384 || K % 4 != 0) return false;
   int c = (N + dev->sm_count - 1) / dev->sm_count;
+  const int nw0 = kBlockGemvThreads / 32;
   int w = 1;
-  while (c * w < 16 && (K / 4) / (w * 2) >= 32) w *= 2;
-  size_t red = (size_t)(c * w > 8 ? c * w : 8) * M;
+  while (c * w < 2 * nw0 && w < 8 && (K / 4) / (w * 2) >= 32) w *= 2;
+  const int nw = kBlockGemvThreads / 32;
+  size_t red = (size_t)(c * w > nw ? c * w : nw) * M;
   size_t bytes = ((size_t)c * K + (size_t)M * K * (layernorm ? 2 : 1) + ((red + 3) & ~size_t(3))) * 4 + 16;
   if (bytes > dev->smem_optin - 2048) return false;
   *cols = c;
@@ -362,7 +364,7 @@ static int32_t launch_gemv_block_t(wgpt_device *dev, const float *x, size_t ldx,
   auto kern = gemv_block_kernel<M>;
   if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = (N + cols - 1) / cols;
-  LAUNCH_PDL(dev, kern, grid, 256, smem, x, ldx, gamma, beta, Wt, K, N, cols, wk, epi, dev->d_err, ap);
+  LAUNCH_PDL(dev, kern, grid, kBlockGemvThreads, smem, x, ldx, gamma, beta, Wt, K, N, cols, wk, epi, dev->d_err, ap);
   return WGPT_OK;
 }
 

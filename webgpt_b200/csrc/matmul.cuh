@@ -235,7 +235,7 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
 // ------------------------------------------------------------------------------------------------
 // LayerNorm of M rows of K floats held in shared memory (normStats + norm, instructions.js:451-550).
 // Every warp computes the two-pass statistics of every row itself (the row is only K floats, and this needs no
-// block-wide barrier); the 256 threads then share the writes of the normalised rows into a second buffer.
+// block-wide barrier); the threads of the CTA then share the writes of the normalised rows into a second buffer.
 // Ends with one __syncthreads(). gamma and beta are weights: the caller loads element tid of each before
 // waiting on the previous kernel, so their memory latency is off the critical path.
 template <int M>
@@ -267,7 +267,7 @@ __device__ __forceinline__ void cta_layernorm_rows(const float *raw, float *norm
     // one division per row; the shader divides every element by sd (instructions.js:544), which differs from
     // multiplying by 1/sd by at most one unit in the last place
     const float rsd = 1.0f / sqrtf(warp_sum(q) / (float)K + 1e-5f);
-    for (int i = tid; i < K4; i += 256) {
+    for (int i = tid; i < K4; i += (int)blockDim.x) {
       float4 v = x4[(size_t)m * K4 + i], g = i == tid ? g_first : g4[i], b = i == tid ? b_first : b4[i];
       o4[(size_t)m * K4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
                                            g.z * ((v.z - mean) * rsd) + b.z, g.w * ((v.w - mean) * rsd) + b.w);
@@ -284,11 +284,13 @@ __device__ __forceinline__ void cta_layernorm_rows(const float *raw, float *norm
 // copies (bounded), multiply out of shared memory. Work items are (column, K slice), wk in {1,2,4,8}; a warp
 // keeps the same K slice for all its items and handles three columns at a time; the K slices of a column are
 // summed in a fixed order.
-// Dynamic shared memory: [cols*K] weights, [M*K] input rows (twice with LayerNorm), [max(cols*wk, 8)*M]
+// Dynamic shared memory: [cols*K] weights, [M*K] input rows (twice with LayerNorm), [max(cols*wk, 16)*M]
 // partial sums, one mbarrier.
 // *err is set (and nothing stored) if the copies do not land within the poll limit.
+constexpr int kBlockGemvThreads = 512;
+
 template <int M>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kBlockGemvThreads)
 gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
                   const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, int cols, int wk,
                   Epilogue epi, int *err, AttnPartials ap) {
@@ -297,7 +299,8 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   float *xs = wbuf + (size_t)cols * K;                                    // input rows as staged
   float *xn = gamma != nullptr ? xs + (size_t)M * K : xs;                // normalised rows (LayerNorm only)
   float *red = xn + (size_t)M * K;
-  const int red_floats = (max(cols * wk, 8) * M + 3) & ~3;
+  constexpr int NT = kBlockGemvThreads, NW = NT / 32;
+  const int red_floats = (max(cols * wk, NW) * M + 3) & ~3;
   uint64_t *bar = reinterpret_cast<uint64_t *>(red + red_floats);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K4 = K >> 2;
@@ -325,7 +328,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   if (has_out && epi.colscale) scale_v = epi.colscale[col0 + oc];
   // All index arithmetic happens here, ahead of the wait (integer division is slow enough to matter after it).
   const int wk_log2 = 31 - __clz(wk);          // wk is a power of two
-  const int ks = warp & (wk - 1);              // 8 % wk == 0: every item of this warp has the same K slice
+  const int ks = warp & (wk - 1);              // NW % wk == 0: every item of this warp has the same K slice
   const int beg = (int)(((unsigned)K4 * (unsigned)ks) >> wk_log2);
   const int end = (int)(((unsigned)K4 * (unsigned)(ks + 1)) >> wk_log2);
   const int items = ncol << wk_log2;
@@ -346,12 +349,12 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     if (ap.part != nullptr) {  // the input rows are attention outputs still split into position slices
 #pragma unroll
       for (int m = 0; m < M; m++)
-        for (int i = tid; i < K4; i += 256) xs4w[(size_t)m * K4 + i] = attn_merged_value4(ap, m, 4 * i);
+        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * K4 + i] = attn_merged_value4(ap, m, 4 * i);
     } else {
 #pragma unroll
       for (int m = 0; m < M; m++)
 #pragma unroll 4
-        for (int i = tid; i < K4; i += 256) xs4w[(size_t)m * K4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
+        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * K4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
     }
   }
   __syncthreads();  // also makes the mbarrier initialisation visible to every thread
@@ -372,12 +375,12 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   const float4 *w4 = reinterpret_cast<const float4 *>(wbuf);
   const float4 *xs4 = reinterpret_cast<const float4 *>(xn);
   constexpr int NB = 3;
-  for (int it0 = warp; it0 < items; it0 += 8 * NB) {
+  for (int it0 = warp; it0 < items; it0 += NW * NB) {
     int c[NB];
     bool valid[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      int it = it0 + 8 * b;
+      int it = it0 + NW * b;
       valid[b] = it < items;
       c[b] = valid[b] ? (it >> wk_log2) : 0;
     }
@@ -411,7 +414,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   }
   trace(2, 5);
   __syncthreads();
-  if (has_out) {  // first 256 outputs: bias / residual were fetched ahead
+  if (has_out) {  // first NT outputs: bias / residual were fetched ahead
     float v = 0.f;
     for (int k = 0; k < wk; k++) v += red[(oc * wk + k) * M + om];
     v = v * scale_v + bias_v;
@@ -419,7 +422,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     if (epi.residual) v += res_v;
     *epi_addr(epi, om, col0 + oc) = v;
   }
-  for (int o = tid + 256; o < ncol * M; o += 256) {
+  for (int o = tid + NT; o < ncol * M; o += NT) {
     const int cc = o / M, m = o - cc * M;
     float v = 0.f;
     for (int k = 0; k < wk; k++) v += red[(cc * wk + k) * M + m];
