@@ -95,6 +95,19 @@ int32_t wgpt_event_destroy(wgpt_device *dev, void *event);
 int32_t wgpt_matmul(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in, const float *W,
                     const float *bias, float *out);
 
+/* FastMatMulBlock (instructions.js:157-319) with the weight stored transposed, Wt[cols, shared] (each output
+ * column's weights contiguous) - the layout the model path keeps after its load-time re-layout
+ * (model.js:362,456-468 re-lay-out at load too). Up to 8 rows stream the weights in FP32; more rows use the
+ * device's precision mode (wgpt_device_set_precision): tensor cores for TF32 / 3xTF32. Same preconditions as
+ * wgpt_matmul. */
+int32_t wgpt_matmul_nk(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in, const float *Wt,
+                       const float *bias, float *out);
+
+/* Waits for the device's stream and reports an error a kernel flagged on the device since the last check
+ * (WGPT_ERR_TIMEOUT: a bounded device-side wait gave up; WGPT_ERR_ARG: a token id was out of range). The
+ * model-level calls do this themselves; the per-operator calls only enqueue. */
+int32_t wgpt_device_check(wgpt_device *dev);
+
 /* No counterpart in the reference. The same product as wgpt_matmul for 1..8 rows, for callers that must not
  * trigger a device allocation: an inference server that has handed all of HBM to its own arena and treats any
  * later cudaMalloc as a budget violation, a latency-critical decode loop (cudaMalloc can serialise against every

@@ -1,0 +1,87 @@
+"""GPU parity of the tcgen05 tensor-core GEMM (TF32 and 3xTF32) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import rel_err
+from webgpt_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL_X3 = 5e-5    # 3 x TF32: the operands are exact to ~2^-21; what remains is the tensor core's own FP32
+                 # accumulation, which truncates, so the error grows with K (measured 2.3e-5 at K = 3072)
+TOL_TF32 = 3e-3  # single TF32 product
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from webgpt_b200 import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+def run_nk(dev, A, Wt, b, mode):
+    from webgpt_b200 import _lib
+    M, K = A.shape
+    N = Wt.shape[0]
+    dev.set_precision(mode)
+    a_d, w_d, b_d, o_d = dev.tensor(A), dev.tensor(Wt), dev.tensor(b), dev.buffer(M * N * 4)
+    try:
+        _lib.call("wgpt_matmul_nk", dev.handle, M, N, K, a_d.ptr, w_d.ptr, b_d.ptr, o_d.ptr)
+        _lib.call("wgpt_device_check", dev.handle)
+        return o_d.read(np.float32, M * N).reshape(M, N)
+    finally:
+        dev.set_precision(_lib.PRECISION_FP32)
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 32, 128), (128, 64, 128), (256, 768, 768), (100, 96, 200), (64, 768, 2304),
+                                   (512, 3072, 768), (333, 1600, 136), (1024, 768, 3072)])
+def test_gemm_tc_matches_oracle(dev, oracle, M, K, N):
+    from webgpt_b200 import _lib
+    rng = np.random.default_rng(M + K + N)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    Wt = (rng.standard_normal((N, K), dtype=np.float32) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    ref = oracle.matmul(A, np.ascontiguousarray(Wt.T), b)
+    got3 = run_nk(dev, A, Wt, b, _lib.PRECISION_TF32X3)
+    assert rel_err(got3, ref) < TOL_X3
+    got1 = run_nk(dev, A, Wt, b, _lib.PRECISION_TF32)
+    assert rel_err(got1, ref) < TOL_TF32
+    got0 = run_nk(dev, A, Wt, b, _lib.PRECISION_FP32)
+    assert rel_err(got0, ref) < 1e-5
+    # deterministic
+    assert np.array_equal(run_nk(dev, A, Wt, b, _lib.PRECISION_TF32X3), got3)
+
+
+def test_gemm_tc_index_pattern(dev):
+    """Small integers are exact in TF32: the product must be bit-exact, which pins tile, swizzle and row/column
+    mapping (any misplaced element changes an integer)."""
+    from webgpt_b200 import _lib
+    M, K, N = 256, 96, 256
+    A = ((np.arange(M)[:, None] * 7 + np.arange(K)[None, :] * 3) % 11 - 5).astype(np.float32)
+    Wt = ((np.arange(N)[:, None] * 5 + np.arange(K)[None, :]) % 13 - 6).astype(np.float32)
+    b = np.arange(N, dtype=np.float32)
+    ref = A.astype(np.float64) @ Wt.astype(np.float64).T + b
+    for mode in (_lib.PRECISION_TF32, _lib.PRECISION_TF32X3):
+        assert np.array_equal(run_nk(dev, A, Wt, b, mode).astype(np.float64), ref)
+
+
+def test_model_in_tf32x3_matches_oracle(oracle):
+    """Prefill and batched decode through the tensor cores: logits within 1e-3 (required) / 5e-5 (asserted)."""
+    from webgpt_b200 import GPT, _lib
+    params = synth.CONFIGS["small"]
+    w = synth.make_weights(params, seed=6, std=0.1, ln_random=True)
+    gpt = GPT(None, params=params, weights=w)
+    gpt.initialize()
+    try:
+        gpt.device.set_precision(_lib.PRECISION_TF32X3)
+        m = oracle.Model(params, synth.weight_list(params, w))
+        ids = synth.make_tokens(params["vocab_size"], 50, seed=4)
+        assert rel_err(gpt.run(ids), m.run(ids)) < 5e-5
+        n_seq = 12
+        prompts = np.stack([synth.make_tokens(params["vocab_size"], 9, seed=20, stream=i) for i in range(n_seq)])
+        batch = gpt.session(n_seq).generate_greedy(prompts, 10)
+        for i in (0, 5, n_seq - 1):
+            assert np.array_equal(batch[i], m.generate_greedy(prompts[i], 10)[9:])
+    finally:
+        gpt.destroy()

@@ -53,6 +53,8 @@ SIGNATURES = {
     "wgpt_event_elapsed_ms": [vp, vp, vp, C.POINTER(f32)],
     "wgpt_event_destroy": [vp, vp],
     "wgpt_matmul": [vp, i32, i32, i32, vp, vp, vp, vp],
+    "wgpt_matmul_nk": [vp, i32, i32, i32, vp, vp, vp, vp],
+    "wgpt_device_check": [vp],
     "wgpt_matmul_static": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_residual": [vp, i32, i32, vp, vp, vp],
     "wgpt_layernorm": [vp, i32, i32, vp, vp, vp, vp],

@@ -16,6 +16,7 @@
 #include "attention.cuh"
 #include "common.cuh"
 #include "elementwise.cuh"
+#include "gemm_tc.cuh"
 #include "int8.cuh"
 #include "matmul.cuh"
 
@@ -193,7 +194,6 @@ WGPT_EXPORT int32_t wgpt_device_synchronize(wgpt_device *dev) {
 WGPT_EXPORT int32_t wgpt_device_set_precision(wgpt_device *dev, int32_t mode) {
   TRY(use(dev));
   REQUIRE(mode >= WGPT_PRECISION_FP32 && mode <= WGPT_PRECISION_TF32, WGPT_ERR_ARG, "unknown precision mode %d", mode);
-  REQUIRE(mode == WGPT_PRECISION_FP32, WGPT_ERR_UNSUPPORTED, "tensor-core precision modes are not built yet");
   dev->precision = mode;
   return WGPT_OK;
 }
@@ -415,6 +415,68 @@ static int32_t launch_gemm_simt(wgpt_device *dev, bool b_nk, const float *A, siz
   return WGPT_OK;
 }
 
+// ---- tensor-core GEMM launch ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tensor map of a row-major FP32 matrix [rows, cols] with row stride ld (floats), boxes of 32 x 128 elements,
+// 128-byte swizzle, zero fill outside the matrix.
+static int32_t make_tile_map(CUtensorMap *map, const float *base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  REQUIRE(fn != nullptr, WGPT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  REQUIRE(r == CUDA_SUCCESS, WGPT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return WGPT_OK;
+}
+
+// C = A[M,K] (row stride lda) . Wt[N,K]^T on the tensor cores; x3 selects 3 x TF32.
+static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t lda, const float *Wt, int M, int K,
+                              int N, const Epilogue &epi) {
+  REQUIRE(aligned16(A) && aligned16(Wt) && (lda % 4) == 0 && (K % 4) == 0, WGPT_ERR_ALIGN,
+          "tensor-core GEMM operands must be 16-byte aligned with row strides that are multiples of 16 bytes");
+  CUtensorMap ma, mb;
+  TRY(make_tile_map(&ma, A, (uint64_t)M, (uint64_t)K, lda));
+  TRY(make_tile_map(&mb, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K));
+  dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
+  if (x3) {
+    auto kern = gemm_tc_kernel<true>;
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
+    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err);
+  } else {
+    auto kern = gemm_tc_kernel<false>;
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
+    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err);
+  }
+  return WGPT_OK;
+}
+
+// Matrix product for more than 8 rows against a weight stored [N,K]: tensor cores or CUDA cores per dev->precision.
+static int32_t launch_gemm_nk(wgpt_device *dev, const float *A, size_t lda, const float *Wt, int M, int K, int N,
+                              const Epilogue &epi) {
+  if (dev->precision == WGPT_PRECISION_FP32) return launch_gemm_simt(dev, true, A, lda, Wt, M, K, N, epi);
+  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, Wt, M, K, N, epi);
+}
+
 static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in, const float *gamma, const float *beta,
                                 float *out, size_t ld_out, int rows, int N) {
   LAUNCH(dev, layernorm_kernel, (rows + 3) / 4, 128, 0, in, ld_in, gamma, beta, out, ld_out, rows, N);
@@ -530,6 +592,27 @@ WGPT_EXPORT int32_t wgpt_matmul(wgpt_device *dev, int32_t rows, int32_t cols, in
   return matmul_kn(dev, rows, shared, cols, in, W, plain_epi(out, cols, bias));
 }
 
+static int32_t check_err_word(wgpt_device *dev, const char *what);
+
+WGPT_EXPORT int32_t wgpt_matmul_nk(wgpt_device *dev, int32_t rows, int32_t cols, int32_t shared, const float *in,
+                                   const float *Wt, const float *bias, float *out) {
+  TRY(use(dev));
+  REQUIRE(in && Wt && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(rows >= 1 && cols >= 1 && shared >= 1, WGPT_ERR_SHAPE, "empty matmul %dx%dx%d", rows, cols, shared);
+  REQUIRE(cols % 8 == 0, WGPT_ERR_SHAPE, "Cols must be divisible by 16.");
+  REQUIRE(shared % 4 == 0, WGPT_ERR_SHAPE, "shared dimension %d must be divisible by 4", shared);
+  REQUIRE(aligned16(in) && aligned16(Wt) && aligned16(out) && aligned16(bias), WGPT_ERR_ALIGN,
+          "buffers must be 16-byte aligned");
+  Epilogue e = plain_epi(out, cols, bias);
+  if (gemv_nk_fits(dev, rows, shared)) return launch_gemv_nk(dev, rows, in, (size_t)shared, nullptr, nullptr, Wt, shared, cols, e);
+  return launch_gemm_nk(dev, in, (size_t)shared, Wt, rows, shared, cols, e);
+}
+
+WGPT_EXPORT int32_t wgpt_device_check(wgpt_device *dev) {
+  TRY(use(dev));
+  return check_err_word(dev, "wgpt_device_check");
+}
+
 WGPT_EXPORT int32_t wgpt_residual(wgpt_device *dev, int32_t rows, int32_t cols, const float *a, const float *b,
                                   float *out) {
   TRY(use(dev));
@@ -581,6 +664,7 @@ static int32_t check_err_word(wgpt_device *dev, const char *what) {
   if (h) {
     CK(cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream));
     if (h == 2) return fail(WGPT_ERR_TIMEOUT, "%s: a bulk copy into shared memory did not complete in time", what);
+    if (h == 3) return fail(WGPT_ERR_TIMEOUT, "%s: the tensor-core GEMM pipeline gave up waiting on a barrier", what);
     return fail(WGPT_ERR_ARG, "%s: token id out of range", what);
   }
   return WGPT_OK;
@@ -971,7 +1055,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
       TRY(launch_layernorm(dev, a, (size_t)K, gamma, beta, s->h, (size_t)K, M, K));
       src = s->h;
     }
-    return launch_gemm_simt(dev, true, src, (size_t)K, Wt, M, K, N, e);
+    return launch_gemm_nk(dev, src, (size_t)K, Wt, M, K, N, e);
   };
 
   for (int l = 0; l < p.n_layer; l++) {
@@ -1035,7 +1119,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     return WGPT_OK;
   }
   TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
-  TRY(launch_gemm_simt(dev, true, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
+  TRY(launch_gemm_nk(dev, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
   if (pick) TRY(pick_and_advance(s, n_tok));
   return WGPT_OK;
 }

@@ -1,0 +1,247 @@
+// Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] . Wt[N,K]^T (+ epilogue), FP32 in and out.
+//
+// One CTA computes a 128 x 128 tile. TMA (cp.async.bulk.tensor, 128-byte swizzle) stages 128 x 32 FP32 tiles of
+// A and of Wt into a ring in shared memory; one thread issues tcgen05.mma kind::tf32 into a 128-lane x
+// 128-column FP32 accumulator in tensor memory; four warps read it back with tcgen05.ld and apply the fused
+// epilogue (bias / GELU / residual / KV scatter).
+//
+// Precision modes:
+//   1 x TF32  - the tensor core reads the FP32 tiles as they are (it uses the top 19 bits of each value).
+//   3 x TF32  - four extra warps split every staged value x into hi = x with the low 13 mantissa bits cleared
+//               (exactly a TF32 number) and lo = x - hi (exact in FP32), and three products are accumulated:
+//               hi*hi + hi*lo + lo*hi. The dropped lo*lo term and the rounding of lo to TF32 are ~2^-21 relative.
+//
+// Roles (warp index): 0 TMA producer, 1 MMA issuer (also owns the tensor-memory allocation), 2-5 epilogue
+// (warp w reads accumulator lanes 32*(w%4)..+31), 6-9 hi/lo split (3 x TF32 only).
+// Every mbarrier wait is bounded; on expiry the CTA raises a shared abort flag, sets *err = 3, drains and exits.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace wgpt {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 32;  // BK * 4 bytes = one 128-byte swizzle row
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 4;      // 16 KiB, A and B tiles alike
+constexpr uint32_t TC_POLLS = 1u << 18;
+
+// ---- tcgen05 / TMA wrappers ----
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_addr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Executed by one whole warp: allocates ncols (power of two >= 32) tensor-memory columns, address -> *slot (smem).
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], issued by one thread.
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+               : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread = lane, register j = column j).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+}
+
+// Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes with the 128-byte swizzle
+// (what TMA writes for a {32 floats, rows} box): start address, stride between 8-row groups = 1024 bytes,
+// descriptor version 1, swizzle mode 2 (128 B). The tile base must be 1024-byte aligned; advancing by k*32
+// bytes inside the swizzle row selects the k-th group of 8 TF32 values.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // bits 0-13: start address >> 4
+  d |= (uint64_t)(1024u >> 4) << 32;              // bits 32-45: stride byte offset >> 4
+  d |= (uint64_t)1 << 46;                         // bits 46-47: descriptor version
+  d |= (uint64_t)2 << 61;                         // bits 61-63: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: FP32 accumulate, TF32 A and B, both K-major, N = TC_BN, M = TC_BM.
+constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+                              ((uint32_t)(TC_BM >> 4) << 24);
+
+
+// Shared-memory plan: [stages][A tile | B tile | (X3: A lo | B lo)] (1024-byte aligned), then the barriers.
+template <bool X3>
+struct TcPlan {
+  static constexpr int kStages = X3 ? 3 : 6;
+  static constexpr int kStageBytes = (X3 ? 4 : 2) * TC_TILE_BYTES;
+  static constexpr int kThreads = X3 ? 320 : 192;
+  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 256;
+};
+
+template <bool X3>
+__global__ void __launch_bounds__(TcPlan<X3>::kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int K,
+               int N, Epilogue epi, int *err) {
+  using Plan = TcPlan<X3>;
+  constexpr int S = Plan::kStages;
+  extern __shared__ uint8_t tc_smem_raw[];
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + (size_t)S * Plan::kStageBytes);
+  uint64_t *full = bars, *empty = bars + S, *ready = bars + 2 * S, *acc_done = bars + 3 * S;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; i++) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+      mbar_init(&ready[i], 128);
+    }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TC_BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  pdl_launch_dependents();
+  pdl_wait();  // A (activations) comes from the previous kernel
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; kb++) {
+        const int s = kb % S, it = kb / S;
+        if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
+        uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
+        mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
+        tma_load_2d(st, &map_a, kb * TC_BK, m0, &full[s]);
+        tma_load_2d(st + TC_TILE_BYTES, &map_b, kb * TC_BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; kb++) {
+        const int s = kb % S, it = kb / S;
+        uint64_t *go = X3 ? &ready[s] : &full[s];
+        if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS)) { *abort_flag = 1; break; }
+        tc_fence_after();
+        const uint32_t a_hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes);
+        const uint32_t b_hi = a_hi + TC_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 8; k++) {
+          const uint64_t da = umma_desc_sw128(a_hi + k * 32), db = umma_desc_sw128(b_hi + k * 32);
+          umma_tf32(tmem_acc, da, db, TC_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          if (X3) {
+            const uint64_t dal = umma_desc_sw128(a_hi + 2 * TC_TILE_BYTES + k * 32);
+            const uint64_t dbl = umma_desc_sw128(b_hi + 2 * TC_TILE_BYTES + k * 32);
+            umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
+            umma_tf32(tmem_acc, dal, db, TC_IDESC, 1u);
+          }
+        }
+        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_done);     // accumulator complete (also reached after an abort, so the epilogue wakes up)
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue: accumulator lanes 32*(warp%4).. ----------------
+    const int quad = warp & 3;
+    const bool ok = mbar_wait(acc_done, 0, TC_POLLS << 4) && !*abort_flag;  // spans the whole main loop
+    if (!ok) *abort_flag = 1;
+    tc_fence_after();
+    if (ok) {
+      const int m = m0 + quad * 32 + lane;
+      const bool vec_ok = ((N | epi.ld) & 3) == 0;
+#pragma unroll 1
+      for (int c = 0; c < TC_BN / 32; c++) {
+        float v[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+        if (m < M) {
+          const int nb = n0 + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int n = nb + j;
+            if (n >= N) break;
+            if (vec_ok) {
+              epi_store4(epi, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), m, n);
+            } else {
+#pragma unroll
+              for (int t = 0; t < 4; t++)
+                if (n + t < N) epi_store(epi, v[j + t], m, n + t);
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (X3) {
+    // ---------------- hi/lo split (warps 6-9) ----------------
+    const int t = threadIdx.x - 6 * 32;  // 0..127
+    for (int kb = 0; kb < num_kb; kb++) {
+      const int s = kb % S, it = kb / S;
+      if (*abort_flag || !mbar_wait(&full[s], it & 1, TC_POLLS)) { *abort_flag = 1; break; }
+      // A and B tiles are adjacent (32 KiB); the lo copies sit 32 KiB further. Element order does not matter.
+      float4 *hi = reinterpret_cast<float4 *>(tiles + (size_t)s * Plan::kStageBytes);
+      float4 *lo = hi + (2 * TC_TILE_BYTES) / 16;
+#pragma unroll 4
+      for (int i = t; i < (2 * TC_TILE_BYTES) / 16; i += 128) {
+        float4 x = hi[i], h, l;
+        h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); l.x = x.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u); l.y = x.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); l.z = x.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u); l.w = x.w - h.w;
+        hi[i] = h;
+        lo[i] = l;
+      }
+      fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
+      mbar_arrive(&ready[s]);
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 3);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, TC_BN);
+  }
+}
+
+}  // namespace wgpt
