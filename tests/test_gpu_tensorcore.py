@@ -31,7 +31,7 @@ def run_nk(dev, A, Wt, b, mode):
         _lib.call("wgpt_device_check", dev.handle)
         return o_d.read(np.float32, M * N).reshape(M, N)
     finally:
-        dev.set_precision(_lib.PRECISION_FP32)
+        dev.set_precision(_lib.PRECISION_TF32X3)
 
 
 @pytest.mark.parametrize("M,K,N", [(128, 32, 128), (128, 64, 128), (256, 768, 768), (100, 96, 200), (64, 768, 2304),

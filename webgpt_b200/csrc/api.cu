@@ -67,6 +67,8 @@ struct wgpt_device {
   void *scratch;  // library-owned workspace (split-K partial sums, temporaries of wgpt_attention)
   size_t scratch_cap;
   int *d_err;     // device-side error word (out-of-range token id)
+  float *tc_scratch;  // split-K partial tiles of the tensor-core GEMM (fixed size)
+  size_t tc_scratch_bytes;
   bool pdl;       // launch the decode-chain kernels with programmatic dependent launch (WGPT_PDL=0 turns it off)
   bool graphs;    // replay decode steps as a CUDA graph (WGPT_GRAPH=0 turns it off)
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
@@ -151,7 +153,7 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
           ordinal, prop.major, prop.minor);
   wgpt_device *dev = new wgpt_device();
   dev->ordinal = ordinal;
-  dev->precision = WGPT_PRECISION_FP32;
+  dev->precision = WGPT_PRECISION_TF32X3;  // FP32-class accuracy on the tensor cores; see wgpt_device_set_precision
   dev->launches = 0;
   dev->sm_count = prop.multiProcessorCount;
   dev->smem_optin = prop.sharedMemPerBlockOptin;
@@ -165,7 +167,10 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
+  dev->tc_scratch = nullptr;
+  dev->tc_scratch_bytes = size_t(64) << 20;
   if (e == cudaSuccess) e = cudaMalloc(&dev->d_err, sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&dev->tc_scratch, dev->tc_scratch_bytes);
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream);
   if (e != cudaSuccess) {
     delete dev;
@@ -180,6 +185,7 @@ WGPT_EXPORT int32_t wgpt_device_destroy(wgpt_device *dev) {
   cudaStreamSynchronize(dev->stream);
   if (dev->scratch) cudaFree(dev->scratch);
   if (dev->d_err) cudaFree(dev->d_err);
+  if (dev->tc_scratch) cudaFree(dev->tc_scratch);
   cudaStreamDestroy(dev->stream);
   delete dev;
   return WGPT_OK;
@@ -457,15 +463,38 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   CUtensorMap ma, mb;
   TRY(make_tile_map(&ma, A, (uint64_t)M, (uint64_t)K, lda));
   TRY(make_tile_map(&mb, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K));
-  dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
+  // Too few 128x128 tiles to occupy the machine (skinny M): split the K loop over CTAs.
+  const int tiles = ((N + TC_BN - 1) / TC_BN) * ((M + TC_BM - 1) / TC_BM);
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  int splits = 1, kb_per_split = total_kb;
+  float *split_out = nullptr;
+  if (tiles * 2 <= dev->sm_count && total_kb > 1 && dev->tc_scratch != nullptr) {
+    int want = (dev->sm_count + tiles - 1) / tiles;
+    if (want > total_kb) want = total_kb;
+    kb_per_split = (total_kb + want - 1) / want;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    if (splits > 1 && (size_t)splits * M * N * 4 <= dev->tc_scratch_bytes && (N % 4) == 0) {
+      split_out = dev->tc_scratch;
+    } else {
+      splits = 1;
+      kb_per_split = total_kb;
+    }
+  }
+  dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM, splits);
   if (x3) {
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
+               kb_per_split, split_out);
   } else {
     auto kern = gemm_tc_kernel<false>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
+               kb_per_split, split_out);
+  }
+  if (split_out != nullptr) {
+    int n4 = M * (N / 4);
+    LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
   }
   return WGPT_OK;
 }

@@ -13,6 +13,7 @@
 //
 // Roles (warp index): 0 TMA producer, 1 MMA issuer (also owns the tensor-memory allocation), 2-5 epilogue
 // (warp w reads accumulator lanes 32*(w%4)..+31), 6-9 hi/lo split (3 x TF32 only).
+// With few output tiles the K loop is split over gridDim.z CTAs (deterministic two-stage sum).
 // Every mbarrier wait is bounded; on expiry the CTA raises a shared abort flag, sets *err = 3, drains and exits.
 #pragma once
 #include <cuda.h>
@@ -111,7 +112,7 @@ struct TcPlan {
 template <bool X3>
 __global__ void __launch_bounds__(TcPlan<X3>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int K,
-               int N, Epilogue epi, int *err) {
+               int N, Epilogue epi, int *err, int kb_per_split, float *split_out) {
   using Plan = TcPlan<X3>;
   constexpr int S = Plan::kStages;
   extern __shared__ uint8_t tc_smem_raw[];
@@ -123,7 +124,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
-  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  // Split-K (few output tiles, e.g. 64-row batched decode): CTA z handles k-blocks [kb0, kb0 + num_kb) and stores
+  // its raw partial tile to split_out[z][M][N]; a second kernel sums the slices in order and applies the epilogue.
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  const int kb0 = blockIdx.z * kb_per_split;
+  const int num_kb = min(kb_per_split, total_kb - kb0);
+  if (split_out != nullptr) {
+    epi.colscale = nullptr; epi.bias = nullptr; epi.residual = nullptr; epi.kc = nullptr; epi.vc = nullptr;
+    epi.act = 0;
+    epi.out = split_out + (size_t)blockIdx.z * M * N;
+    epi.ld = N;
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; i++) {
@@ -152,8 +163,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
         uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
         mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
-        tma_load_2d(st, &map_a, kb * TC_BK, m0, &full[s]);
-        tma_load_2d(st + TC_TILE_BYTES, &map_b, kb * TC_BK, n0, &full[s]);
+        tma_load_2d(st, &map_a, (kb0 + kb) * TC_BK, m0, &full[s]);
+        tma_load_2d(st + TC_TILE_BYTES, &map_b, (kb0 + kb) * TC_BK, n0, &full[s]);
       }
     }
   } else if (warp == 1) {
