@@ -168,3 +168,43 @@ def test_tap_is_pre_lnf_residual_stream(oracle):
         assert rel_err(got, taps[-2]) < TIGHT
     finally:
         gpt.destroy()
+
+
+def test_xl_shape_two_layers(oracle):
+    """GPT-2 XL geometry (d=1600, 25 heads of 64, 4d=6400) cut to two layers and a small vocabulary: exercises
+    K = 1600 / 6400 (not multiples of 128), the register-streaming GEMV where a block does not fit shared memory,
+    and 25 heads, in prefill (tensor cores), single-token decode and a 3-sequence batch."""
+    params = dict(n_layer=2, n_head=25, n_embd=1600, n_ctx=96, vocab_size=1000)
+    w = synth.make_weights(params, seed=11, std=0.05, ln_random=True)
+    gpt = make_gpt(params, w)
+    try:
+        m = oracle.Model(params, synth.weight_list(params, w))
+        ids = synth.make_tokens(params["vocab_size"], 70, seed=12)
+        assert rel_err(gpt.run(ids), m.run(ids)) < TIGHT
+        s = gpt.session()
+        s.reset()
+        s.forward(ids[:66], want_logits=False)
+        for t in range(66, 70):
+            lg = s.forward(ids[t:t + 1])[0]
+        assert rel_err(lg, m.run(ids)) < TIGHT
+        prompts = np.stack([synth.make_tokens(params["vocab_size"], 5, seed=13, stream=i) for i in range(3)])
+        got = gpt.session(3).generate_greedy(prompts, 6)
+        for i in range(3):
+            assert np.array_equal(got[i], m.generate_greedy(prompts[i], 6)[5:])
+    finally:
+        gpt.destroy()
+
+
+def test_generate_longer_than_context_from_long_prompt(oracle):
+    """Prompt longer than n_ctx: the first window is the newest n_ctx tokens and every step slides (model.js:69)."""
+    params = synth.CONFIGS["tiny"]
+    w = synth.make_weights(params, seed=21, std=0.2, ln_random=True)
+    gpt = make_gpt(params, w)
+    try:
+        m = oracle.Model(params, synth.weight_list(params, w))
+        prompt = synth.make_tokens(params["vocab_size"], params["n_ctx"] + 7, seed=22)
+        want = m.generate_greedy(prompt, 5)[len(prompt):]
+        got = gpt.session().generate_greedy(prompt, 5)[0]
+        assert np.array_equal(got, want)
+    finally:
+        gpt.destroy()
