@@ -88,6 +88,17 @@ int32_t wgpt_event_record(wgpt_device *dev, void *event);
 int32_t wgpt_event_elapsed_ms(wgpt_device *dev, void *start, void *stop, float *ms);
 int32_t wgpt_event_destroy(wgpt_device *dev, void *event);
 
+/* ---- pass-list replay: the reference encodes its whole pass list into one command buffer and submits it once
+ *      (model.js:245-257). Between wgpt_graph_begin and wgpt_graph_end the per-operator calls below are recorded
+ *      instead of executed; wgpt_graph_launch replays the recording (a CUDA graph) with one submission. Only the
+ *      enqueue-only calls may be recorded (the per-operator entry points and wgpt_buffer_copy); buffers must stay
+ *      alive and in place; run the same calls once before recording so that library workspaces have their size. */
+typedef struct wgpt_graph wgpt_graph;
+int32_t wgpt_graph_begin(wgpt_device *dev);
+int32_t wgpt_graph_end(wgpt_device *dev, wgpt_graph **out);
+int32_t wgpt_graph_launch(wgpt_device *dev, wgpt_graph *graph);
+int32_t wgpt_graph_destroy(wgpt_device *dev, wgpt_graph *graph);
+
 /* ---- per-operator entry points: one per instruction class of instructions.js ---- */
 
 /* FastMatMulBlock.newInstance(rows, cols, shared, input, weights, bias) (instructions.js:157-177),

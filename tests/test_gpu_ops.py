@@ -170,3 +170,39 @@ def test_int8_unpack_bit_exact(dev, K):
         _lib.call("wgpt_int8_matmul", dev.handle, M, K, N, a_d.ptr, b_d.ptr, s_d.ptr, out.ptr)
         got = out.read(np.float32, M * N).reshape(M, N)
         assert np.array_equal(got, q[:M].astype(np.float32))
+
+
+def test_pass_list_graph_replay(dev, ops, oracle):
+    """A recorded pass list (wgpt_graph_*) replays to the same bits as eager execution, also after the inputs
+    change in place (the recording holds addresses, not values)."""
+    import ctypes as C
+    from webgpt_b200 import _lib
+    rng = np.random.default_rng(9)
+    M, K, N = 4, 384, 768
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    W = (rng.standard_normal((K, N), dtype=np.float32) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    a_d, w_d, b_d, y_d, z_d = dev.tensor(A), dev.tensor(W), dev.tensor(b), dev.buffer(M * N * 4), dev.buffer(M * N * 4)
+
+    def passes():
+        _lib.call("wgpt_matmul", dev.handle, M, N, K, a_d.ptr, w_d.ptr, b_d.ptr, y_d.ptr)
+        _lib.call("wgpt_gelu", dev.handle, M, N, y_d.ptr, z_d.ptr)
+
+    passes()
+    eager = z_d.read(np.float32, M * N)
+    _lib.call("wgpt_graph_begin", dev.handle)
+    passes()
+    g = C.c_void_p()
+    _lib.call("wgpt_graph_end", dev.handle, C.byref(g))
+    z_d.write(np.zeros(M * N, np.float32))
+    _lib.call("wgpt_graph_launch", dev.handle, g)
+    assert np.array_equal(z_d.read(np.float32, M * N), eager)
+    A2 = (A * 0.5).astype(np.float32)
+    a_d.write(A2)
+    _lib.call("wgpt_graph_launch", dev.handle, g)
+    ref = oracle.gelu(oracle.matmul(A2, W, b))
+    assert rel_err(z_d.read(np.float32, M * N).reshape(M, N), ref) < TOL
+    _lib.call("wgpt_graph_destroy", dev.handle, g)
+    with pytest.raises(_lib.WgptError) as e:
+        _lib.call("wgpt_graph_end", dev.handle, C.byref(g))
+    assert e.value.code == _lib.ERR_STATE

@@ -52,6 +52,10 @@ SIGNATURES = {
     "wgpt_event_record": [vp, vp],
     "wgpt_event_elapsed_ms": [vp, vp, vp, C.POINTER(f32)],
     "wgpt_event_destroy": [vp, vp],
+    "wgpt_graph_begin": [vp],
+    "wgpt_graph_end": [vp, vpp],
+    "wgpt_graph_launch": [vp, vp],
+    "wgpt_graph_destroy": [vp, vp],
     "wgpt_matmul": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_matmul_nk": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_device_check": [vp],

@@ -71,6 +71,8 @@ struct wgpt_device {
   size_t tc_scratch_bytes;
   bool pdl;       // launch the decode-chain kernels with programmatic dependent launch (WGPT_PDL=0 turns it off)
   bool graphs;    // replay decode steps as a CUDA graph (WGPT_GRAPH=0 turns it off)
+  bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
+  uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
 };
 
@@ -126,6 +128,8 @@ static int32_t use(wgpt_device *dev) {
 // Grows the workspace. Work already enqueued may still be using the old block, so drain first.
 static int32_t scratch_reserve(wgpt_device *dev, size_t bytes) {
   if (bytes <= dev->scratch_cap) return WGPT_OK;
+  REQUIRE(!dev->capturing, WGPT_ERR_STATE,
+          "the workspace would have to grow while a pass list is being recorded: run the pass list once first");
   CK(cudaStreamSynchronize(dev->stream));
   if (dev->scratch) CK(cudaFree(dev->scratch));
   dev->scratch = nullptr;
@@ -166,6 +170,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->graphs = !(ev && ev[0] == '0');
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
+  dev->capturing = false;
+  dev->capture_launch0 = 0;
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
   dev->tc_scratch = nullptr;
   dev->tc_scratch_bytes = size_t(64) << 20;
@@ -289,6 +295,60 @@ WGPT_EXPORT int32_t wgpt_event_elapsed_ms(wgpt_device *dev, void *start, void *s
 WGPT_EXPORT int32_t wgpt_event_destroy(wgpt_device *dev, void *event) {
   TRY(use(dev));
   if (event) CK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return WGPT_OK;
+}
+
+// ------------------------------------------------------------------------------------------ pass-list graphs
+struct wgpt_graph {
+  cudaGraphExec_t exec;
+  uint64_t launches;
+};
+
+WGPT_EXPORT int32_t wgpt_graph_begin(wgpt_device *dev) {
+  TRY(use(dev));
+  REQUIRE(!dev->capturing, WGPT_ERR_STATE, "a pass list is already being recorded on this device");
+  CK(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed));
+  dev->capturing = true;
+  dev->capture_launch0 = dev->launches;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_graph_end(wgpt_device *dev, wgpt_graph **out) {
+  TRY(use(dev));
+  REQUIRE(out != nullptr, WGPT_ERR_ARG, "out is null");
+  *out = nullptr;
+  REQUIRE(dev->capturing, WGPT_ERR_STATE, "no pass list is being recorded on this device");
+  dev->capturing = false;
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(dev->stream, &g);
+  uint64_t n = dev->launches - dev->capture_launch0;
+  dev->launches = dev->capture_launch0;  // recording enqueued nothing
+  if (e != cudaSuccess) return fail(WGPT_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+  cudaGraphExec_t ex = nullptr;
+  e = cudaGraphInstantiate(&ex, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return fail(WGPT_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+  wgpt_graph *gr = new wgpt_graph();
+  gr->exec = ex;
+  gr->launches = n;
+  *out = gr;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_graph_launch(wgpt_device *dev, wgpt_graph *graph) {
+  TRY(use(dev));
+  REQUIRE(graph != nullptr, WGPT_ERR_ARG, "graph handle is null");
+  CK(cudaGraphLaunch(graph->exec, dev->stream));
+  dev->launches += graph->launches;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_graph_destroy(wgpt_device *dev, wgpt_graph *graph) {
+  TRY(use(dev));
+  if (!graph) return WGPT_OK;
+  CK(cudaStreamSynchronize(dev->stream));
+  cudaGraphExecDestroy(graph->exec);
+  delete graph;
   return WGPT_OK;
 }
 
