@@ -540,17 +540,18 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
       kb_per_split = total_kb;
     }
   }
-  dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM, splits);
+  const int n_work = tiles * splits;
+  dim3 grid(n_work < dev->sm_count ? n_work : dev->sm_count);
   if (x3) {
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
     LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
-               kb_per_split, split_out);
+               kb_per_split, splits, split_out);
   } else {
     auto kern = gemm_tc_kernel<false>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
     LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
-               kb_per_split, split_out);
+               kb_per_split, splits, split_out);
   }
   if (split_out != nullptr) {
     int n4 = M * (N / 4);

@@ -1,15 +1,16 @@
 // Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] . Wt[N,K]^T (+ epilogue), FP32 in and out.
 //
-// One CTA computes a 128 x 128 tile. TMA (cp.async.bulk.tensor, 128-byte swizzle) stages 128 x 32 FP32 tiles of
+// Persistent CTAs (one per SM) each compute a sequence of 128 x 128 tiles. TMA (cp.async.bulk.tensor, 128-byte swizzle) stages 128 x 32 FP32 tiles of
 // A and of Wt into a ring in shared memory; one thread issues tcgen05.mma kind::tf32 into a 128-lane x
-// 128-column FP32 accumulator in tensor memory; four warps read it back with tcgen05.ld and apply the fused
+// 128-column FP32 accumulator in tensor memory (two of them alternate, so a tile's epilogue overlaps the next
+// tile's main loop); four warps read it back with tcgen05.ld and apply the fused
 // epilogue (bias / GELU / residual / KV scatter).
 //
 // Precision modes:
 //   1 x TF32  - the tensor core reads the FP32 tiles as they are (it uses the top 19 bits of each value).
-//   3 x TF32  - four extra warps split every staged value x into hi = x with the low 13 mantissa bits cleared
-//               (exactly a TF32 number) and lo = x - hi (exact in FP32), and three products are accumulated:
-//               hi*hi + hi*lo + lo*hi. The dropped lo*lo term and the rounding of lo to TF32 are ~2^-21 relative.
+//   3 x TF32  - with hi = x truncated to TF32 (what the tensor core sees when it reads x) four extra warps write
+//               lo = x - hi (exact in FP32) next to every staged tile, and three products are accumulated:
+//               hi*hi + hi*lo + lo*hi. The dropped lo*lo term and the truncation of lo are ~2^-21 relative.
 //
 // Roles (warp index): 0 TMA producer, 1 MMA issuer (also owns the tensor-memory allocation), 2-5 epilogue
 // (warp w reads accumulator lanes 32*(w%4)..+31), 6-9 hi/lo split (3 x TF32 only).
@@ -106,35 +107,47 @@ struct TcPlan {
   static constexpr int kStages = X3 ? 3 : 6;
   static constexpr int kStageBytes = (X3 ? 4 : 2) * TC_TILE_BYTES;
   static constexpr int kThreads = X3 ? 320 : 192;
-  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 256;
+  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 512;
 };
 
+// Work item w of a launch: output tile (m_tile, n_tile) and K slice z, tiles of one K slice enumerated with the
+// M tile fastest so that CTAs working side by side share the weight tile.
+struct TcWork {
+  int m0, n0, kb0, num_kb, z;
+};
+__device__ __forceinline__ TcWork tc_work(int w, int m_tiles, int n_tiles, int kb_per_split, int total_kb) {
+  TcWork t;
+  const int per_z = m_tiles * n_tiles;
+  t.z = w / per_z;
+  const int r = w - t.z * per_z;
+  const int nt = r / m_tiles, mt = r - nt * m_tiles;
+  t.m0 = mt * TC_BM;
+  t.n0 = nt * TC_BN;
+  t.kb0 = t.z * kb_per_split;
+  t.num_kb = min(kb_per_split, total_kb - t.kb0);
+  return t;
+}
+
+// Persistent: gridDim.x CTAs (one per SM) walk the work items w = blockIdx.x, blockIdx.x + gridDim.x, ...
+// Two accumulators in tensor memory alternate, so the epilogue of one tile overlaps the main loop of the next.
 template <bool X3>
 __global__ void __launch_bounds__(TcPlan<X3>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int K,
-               int N, Epilogue epi, int *err, int kb_per_split, float *split_out) {
+               int N, Epilogue epi, int *err, int kb_per_split, int splits, float *split_out) {
   using Plan = TcPlan<X3>;
   constexpr int S = Plan::kStages;
   extern __shared__ uint8_t tc_smem_raw[];
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + (size_t)S * Plan::kStageBytes);
-  uint64_t *full = bars, *empty = bars + S, *ready = bars + 2 * S, *acc_done = bars + 3 * S;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+  uint64_t *full = bars, *empty = bars + S, *ready = bars + 2 * S;
+  uint64_t *acc_full = bars + 3 * S, *acc_empty = bars + 3 * S + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
-  // Split-K (few output tiles, e.g. 64-row batched decode): CTA z handles k-blocks [kb0, kb0 + num_kb) and stores
-  // its raw partial tile to split_out[z][M][N]; a second kernel sums the slices in order and applies the epilogue.
   const int total_kb = (K + TC_BK - 1) / TC_BK;
-  const int kb0 = blockIdx.z * kb_per_split;
-  const int num_kb = min(kb_per_split, total_kb - kb0);
-  if (split_out != nullptr) {
-    epi.colscale = nullptr; epi.bias = nullptr; epi.residual = nullptr; epi.kc = nullptr; epi.vc = nullptr;
-    epi.act = 0;
-    epi.out = split_out + (size_t)blockIdx.z * M * N;
-    epi.ld = N;
-  }
+  const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + TC_BN - 1) / TC_BN;
+  const int n_work = m_tiles * n_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; i++) {
@@ -142,15 +155,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&empty[i], 1);
       mbar_init(&ready[i], 128);
     }
-    mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
     *abort_flag = 0;
     fence_async_smem();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TC_BN);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * TC_BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   pdl_launch_dependents();
   pdl_wait();  // A (activations) comes from the previous kernel
@@ -158,65 +174,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; kb++) {
-        const int s = kb % S, it = kb / S;
-        if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
-        uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
-        mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
-        tma_load_2d(st, &map_a, (kb0 + kb) * TC_BK, m0, &full[s]);
-        tma_load_2d(st + TC_TILE_BYTES, &map_b, (kb0 + kb) * TC_BK, n0, &full[s]);
+      int kc = 0;  // k-blocks issued so far by this CTA: stage = kc % S, use = kc / S
+      for (int w = blockIdx.x; w < n_work && !*abort_flag; w += gridDim.x) {
+        const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
+        for (int kb = 0; kb < t.num_kb; kb++, kc++) {
+          const int s = kc % S, it = kc / S;
+          if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
+          uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
+          mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
+          tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[s]);
+          tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; kb++) {
-        const int s = kb % S, it = kb / S;
-        uint64_t *go = X3 ? &ready[s] : &full[s];
-        if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS)) { *abort_flag = 1; break; }
+      int kc = 0, i = 0;  // i: work items done by this CTA; accumulator = i & 1, its use count = i >> 1
+      for (int w = blockIdx.x; w < n_work && !*abort_flag; w += gridDim.x, i++) {
+        const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
+        const int buf = i & 1, use = i >> 1;
+        if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, TC_POLLS << 4)) { *abort_flag = 1; break; }
         tc_fence_after();
-        const uint32_t a_hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes);
-        const uint32_t b_hi = a_hi + TC_TILE_BYTES;
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TC_BN);
+        for (int kb = 0; kb < t.num_kb; kb++, kc++) {
+          const int s = kc % S, it = kc / S;
+          uint64_t *go = X3 ? &ready[s] : &full[s];
+          if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS)) { *abort_flag = 1; break; }
+          tc_fence_after();
+          const uint32_t a_hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes);
+          const uint32_t b_hi = a_hi + TC_TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < TC_BK / 8; k++) {
-          const uint64_t da = umma_desc_sw128(a_hi + k * 32), db = umma_desc_sw128(b_hi + k * 32);
-          umma_tf32(tmem_acc, da, db, TC_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-          if (X3) {
-            const uint64_t dal = umma_desc_sw128(a_hi + 2 * TC_TILE_BYTES + k * 32);
-            const uint64_t dbl = umma_desc_sw128(b_hi + 2 * TC_TILE_BYTES + k * 32);
-            umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
-            umma_tf32(tmem_acc, dal, db, TC_IDESC, 1u);
+          for (int k = 0; k < TC_BK / 8; k++) {
+            const uint64_t da = umma_desc_sw128(a_hi + k * 32), db = umma_desc_sw128(b_hi + k * 32);
+            umma_tf32(tmem_acc, da, db, TC_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            if (X3) {
+              const uint64_t dal = umma_desc_sw128(a_hi + 2 * TC_TILE_BYTES + k * 32);
+              const uint64_t dbl = umma_desc_sw128(b_hi + 2 * TC_TILE_BYTES + k * 32);
+              umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
+              umma_tf32(tmem_acc, dal, db, TC_IDESC, 1u);
+            }
           }
+          umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
-        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        umma_commit(&acc_full[buf]);  // this tile's accumulator is complete (also reached after an abort)
       }
-      umma_commit(acc_done);     // accumulator complete (also reached after an abort, so the epilogue wakes up)
     }
   } else if (warp < 6) {
     // ---------------- epilogue: accumulator lanes 32*(warp%4).. ----------------
     const int quad = warp & 3;
-    const bool ok = mbar_wait(acc_done, 0, TC_POLLS << 4) && !*abort_flag;  // spans the whole main loop
-    if (!ok) *abort_flag = 1;
-    tc_fence_after();
-    if (ok) {
-      const int m = m0 + quad * 32 + lane;
-      const bool vec_ok = ((N | epi.ld) & 3) == 0;
+    int i = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, i++) {
+      const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
+      const int buf = i & 1, use = i >> 1;
+      const bool ok = mbar_wait(&acc_full[buf], use & 1, TC_POLLS << 4) && !*abort_flag;
+      if (!ok) { *abort_flag = 1; break; }
+      tc_fence_after();
+      Epilogue e = epi;
+      if (split_out != nullptr) {  // raw partial tile of K slice z; a second kernel sums the slices in order
+        e.colscale = nullptr; e.bias = nullptr; e.residual = nullptr; e.kc = nullptr; e.vc = nullptr;
+        e.act = 0;
+        e.out = split_out + (size_t)t.z * M * N;
+        e.ld = N;
+      }
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TC_BN);
+      const int m = t.m0 + quad * 32 + lane;
+      const bool vec_ok = ((N | e.ld) & 3) == 0;
 #pragma unroll 1
       for (int c = 0; c < TC_BN / 32; c++) {
         float v[32];
         tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+        if (c == TC_BN / 32 - 1) {  // everything is in registers: hand the accumulator back before storing
+          tc_fence_before();
+          mbar_arrive(&acc_empty[buf]);
+        }
         if (m < M) {
-          const int nb = n0 + c * 32;
+          const int nb = t.n0 + c * 32;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const int n = nb + j;
             if (n >= N) break;
             if (vec_ok) {
-              epi_store4(epi, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), m, n);
+              epi_store4(e, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), m, n);
             } else {
 #pragma unroll
-              for (int t = 0; t < 4; t++)
-                if (n + t < N) epi_store(epi, v[j + t], m, n + t);
+              for (int q = 0; q < 4; q++)
+                if (n + q < N) epi_store(e, v[j + q], m, n + q);
             }
           }
         }
@@ -225,25 +268,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
   } else if (X3) {
     // ---------------- hi/lo split (warps 6-9) ----------------
-    const int t = threadIdx.x - 6 * 32;  // 0..127
-    for (int kb = 0; kb < num_kb; kb++) {
-      const int s = kb % S, it = kb / S;
-      if (*abort_flag || !mbar_wait(&full[s], it & 1, TC_POLLS)) { *abort_flag = 1; break; }
-      // A and B tiles are adjacent (32 KiB); the lo copies sit 32 KiB further. Element order does not matter.
-      float4 *hi = reinterpret_cast<float4 *>(tiles + (size_t)s * Plan::kStageBytes);
-      float4 *lo = hi + (2 * TC_TILE_BYTES) / 16;
+    const int tix = threadIdx.x - 6 * 32;  // 0..127
+    int kc = 0;
+    for (int w = blockIdx.x; w < n_work && !*abort_flag; w += gridDim.x) {
+      const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
+      for (int kb = 0; kb < t.num_kb; kb++, kc++) {
+        const int s = kc % S, it = kc / S;
+        if (*abort_flag || !mbar_wait(&full[s], it & 1, TC_POLLS)) { *abort_flag = 1; break; }
+        // A and B tiles are adjacent (32 KiB); the lo copies sit 32 KiB further. Element order does not matter.
+        float4 *hi = reinterpret_cast<float4 *>(tiles + (size_t)s * Plan::kStageBytes);
+        float4 *lo = hi + (2 * TC_TILE_BYTES) / 16;
 #pragma unroll 4
-      for (int i = t; i < (2 * TC_TILE_BYTES) / 16; i += 128) {
-        float4 x = hi[i], h, l;
-        h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); l.x = x.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u); l.y = x.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); l.z = x.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u); l.w = x.w - h.w;
-        hi[i] = h;
-        lo[i] = l;
+        for (int q = tix; q < (2 * TC_TILE_BYTES) / 16; q += 128) {
+          // kind::tf32 reads the top 19 bits of each FP32 operand and ignores the rest (checked on B200: clearing
+          // the low 13 bits first gives bit-identical products), so the staged tile itself serves as `hi`.
+          float4 x = hi[q], l;
+          l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+          l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+          l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+          l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+          lo[q] = l;
+        }
+        fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
+        mbar_arrive(&ready[s]);
       }
-      fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
-      mbar_arrive(&ready[s]);
     }
   }
 
@@ -251,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 3);
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, TC_BN);
+    tmem_dealloc(tmem_base, 2 * TC_BN);
   }
 }
 
