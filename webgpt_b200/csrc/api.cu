@@ -555,7 +555,7 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   }
   if (split_out != nullptr) {
     int n4 = M * (N / 4);
-    LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
+    LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
   }
   return WGPT_OK;
 }
@@ -569,7 +569,7 @@ static int32_t launch_gemm_nk(wgpt_device *dev, const float *A, size_t lda, cons
 
 static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in, const float *gamma, const float *beta,
                                 float *out, size_t ld_out, int rows, int N) {
-  LAUNCH(dev, layernorm_kernel, (rows + 3) / 4, 128, 0, in, ld_in, gamma, beta, out, ld_out, rows, N);
+  LAUNCH_PDL(dev, layernorm_kernel, (rows + 3) / 4, 128, 0, in, ld_in, gamma, beta, out, ld_out, rows, N);
   return WGPT_OK;
 }
 
@@ -609,7 +609,7 @@ static int32_t gemv_kn_with_scratch(wgpt_device *dev, int M, const float *x, con
     default: return fail(WGPT_ERR_SHAPE, "gemv rows %d out of range", M);
   }
   int n4 = M * (N / 4);
-  LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, epi);
+  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, epi);
   return WGPT_OK;
 }
 
@@ -859,7 +859,7 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
 #undef CASE_W
 #undef CASE_N
   int n4 = M * (N / 4);
-  LAUNCH(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, e);
+  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, e);
   return WGPT_OK;
 }
 

@@ -34,18 +34,20 @@ __global__ void layernorm_kernel(const float *__restrict__ in, size_t ld_in, con
                                  int N) {
   int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   int lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();  // the rows come from the previous kernel (read through L2, see common.cuh)
   if (row >= rows) return;
   const float4 *x = reinterpret_cast<const float4 *>(in + (size_t)row * ld_in);
   int n4 = N >> 2;
   float s = 0.f;
   for (int i = lane; i < n4; i += 32) {
-    float4 v = x[i];
+    float4 v = __ldcg(x + i);
     s += (v.x + v.y) + (v.z + v.w);
   }
   float mean = warp_sum(s) / (float)N;
   float q = 0.f;
   for (int i = lane; i < n4; i += 32) {
-    float4 v = x[i];
+    float4 v = __ldcg(x + i);
     float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
     q += (a * a + b * b) + (c * c + d * d);
   }
@@ -54,7 +56,7 @@ __global__ void layernorm_kernel(const float *__restrict__ in, size_t ld_in, con
   const float4 *b4 = reinterpret_cast<const float4 *>(beta);
   float4 *o = reinterpret_cast<float4 *>(out + (size_t)row * ld_out);
   for (int i = lane; i < n4; i += 32) {
-    float4 v = x[i], g = g4[i], b = b4[i];
+    float4 v = __ldcg(x + i), g = g4[i], b = b4[i];
     o[i] = make_float4(g.x * ((v.x - mean) / sd) + b.x, g.y * ((v.y - mean) / sd) + b.y,
                        g.z * ((v.z - mean) / sd) + b.z, g.w * ((v.w - mean) / sd) + b.w);
   }

@@ -488,11 +488,14 @@ gemv_kn_partial_kernel(const float *__restrict__ x, const float *__restrict__ W,
 __global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit, int M, int N, Epilogue epi) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;  // float4 index over [M, N/4]
   int N4 = N >> 2;
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the previous kernel
   if (i >= M * N4) return;
   int m = i / N4, n = (i - m * N4) * 4;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
   for (int k = 0; k < ksplit; k++) {
-    float4 v = *reinterpret_cast<const float4 *>(part + ((size_t)k * M + m) * N + n);
+    float4 v = __ldcg(reinterpret_cast<const float4 *>(part + ((size_t)k * M + m) * N + n));
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
   epi_store4(epi, s, m, n);
