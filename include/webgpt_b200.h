@@ -234,6 +234,12 @@ int32_t wgpt_session_get_new_ids(wgpt_session *session, int32_t n_new, uint32_t 
  * forward ([rows, n_embd], rows = n_seq * tokens of that call) into dst (device memory). */
 int32_t wgpt_session_tap(wgpt_session *session, float *dst, uint64_t max_floats, uint64_t *floats_written);
 
+/* Visuals.render (visuals.js:213-236) without a canvas: the fragment shader fsMain / hdrColorMapping
+ * (visuals.js:104-135) applied to the buffer the model's externalBuffer tap fills ([n_ctx, n_embd] floats,
+ * model.js:211-222), one pixel per element, into rgba_out (device memory, n_ctx * n_embd * 4 bytes, RGBA8). */
+int32_t wgpt_visuals_render(wgpt_device *dev, const float *embeddings, int32_t n_ctx, int32_t n_embd,
+                            uint8_t *rgba_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -508,6 +508,22 @@ ORC_API int orc_kv_generate_greedy(orc_kv *s, const uint32_t *prompt, int n_prom
   return 0;
 }
 
+/* Visualiser fragment shader, visuals.js:104-135: pixel (x,y) reads buf[y*n_embd + x] (the canvas is n_embd x
+ * n_ctx pixels and fragCoord is the pixel centre, :105-110), v = 0.1*value (:115); hdrColorMapping with threshold 1
+ * (:120-135): v<0 -> b=-v, and g=-v-1 below -1; else r=v, and g=v-1 above 1; g=min(g,0.7). The vec4 starts at
+ * zero, so alpha stays 0. The 8-bit unorm target clamps to [0,1] and rounds to nearest. out: n*4 bytes RGBA. */
+ORC_API void orc_heatmap(const float *buf, size_t n, uint8_t *out) {
+  for (size_t i = 0; i < n; i++) {
+    float v = buf[i] * 0.1f, r = 0.f, g = 0.f, b = 0.f;
+    if (v < 0.f) { b = -v; if (v < -1.0f) g = -v - 1.0f; }
+    else { r = v; if (v > 1.0f) g = v - 1.0f; }
+    g = fminf(g, 0.7f);
+    float c[3] = {r, g, b};
+    for (int k = 0; k < 3; k++) out[4 * i + k] = (uint8_t)floorf(fminf(fmaxf(c[k], 0.f), 1.f) * 255.f + 0.5f);
+    out[4 * i + 3] = 0;
+  }
+}
+
 /* Caps the OpenMP team. A container may see every core of the host while being allowed only a few. */
 ORC_API void orc_set_threads(int n) {
 #ifdef _OPENMP

@@ -201,6 +201,14 @@ def int8_matmul(A, Bq, scale, N, literal=False):
     return out
 
 
+def heatmap(buf):
+    buf, pb = _f(buf)
+    out = np.empty(buf.shape + (4,), np.uint8)
+    lib().orc_heatmap.argtypes = [f32p, C.c_size_t, C.POINTER(C.c_uint8)]
+    lib().orc_heatmap(pb, buf.size, out.ctypes.data_as(C.POINTER(C.c_uint8)))
+    return out
+
+
 TENSORS_PER_LAYER = 12
 
 

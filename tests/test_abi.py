@@ -95,3 +95,25 @@ def test_load_parameters_checks():
         p.update(bad)
         with pytest.raises(ValueError, match=msg):
             GPT(None, params=p).loadParameters(None)
+
+
+def test_weight_folder_round_trip(tmp_path):
+    """The reference's on-disk format: raw little-endian f32 per tensor + params_gpt.json."""
+    import json
+    from webgpt_b200 import globals as G, synth
+    from webgpt_b200.model import GPT
+    params = synth.CONFIGS["tiny"]
+    w = synth.make_weights(params, seed=8, ln_random=True)
+    folder = str(tmp_path / "tiny_model")
+    synth.write_weight_folder(folder, params, w)
+    assert len(os.listdir(folder)) == 1 + 4 + 12 * params["n_layer"]
+    for name in synth.tensor_names(params):
+        back = G.fetchBin(os.path.join(folder, f"{name}_gpt.bin"))
+        assert back.dtype == np.float32 and np.array_equal(back, w[name].ravel())
+    loaded = GPT(folder).loadParameters(folder)
+    assert {k: loaded[k] for k in params} == params
+    # HF-style config without n_ctx
+    p2 = dict(json.load(open(os.path.join(folder, "params_gpt.json"))))
+    p2["n_positions"] = p2.pop("n_ctx")
+    json.dump(p2, open(os.path.join(folder, "params_gpt.json"), "w"))
+    assert GPT(folder).loadParameters(folder)["n_ctx"] == params["n_ctx"]

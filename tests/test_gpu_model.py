@@ -208,3 +208,48 @@ def test_generate_longer_than_context_from_long_prompt(oracle):
         assert np.array_equal(got, want)
     finally:
         gpt.destroy()
+
+
+def test_visuals_heatmap_matches_oracle(oracle, tmp_path):
+    """Visuals.render: the tap of the last run coloured by the reference's fragment-shader arithmetic, bit-exact."""
+    from webgpt_b200.visuals import Visuals
+    g, params, w, gpt = golden_model("gpt2_small.npz")
+    try:
+        vis = Visuals(gpt)
+        vis.init()
+        gpt.run(g["prompt"])
+        img = vis.render(ppm_path=str(tmp_path / "v.ppm"))
+        m = oracle.Model(params, synth.weight_list(params, w))
+        _, taps = m.run(g["prompt"], taps=True)
+        T = len(g["prompt"])
+        tap = gpt.session().tap()
+        assert np.array_equal(img[:T], oracle.heatmap(tap))          # same bytes for the same floats
+        assert np.mean(img[:T] != oracle.heatmap(taps[-2])) < 1e-3   # and for the oracle's own residual stream
+        assert not img[T:].any()
+        assert (tmp_path / "v.ppm").stat().st_size == len(b"P6\n128 64\n255\n") + 64 * 128 * 3
+        # scaled inputs reach every branch of the colour map
+        big = (np.random.default_rng(0).standard_normal((params["n_ctx"], params["n_embd"])) * 12).astype(np.float32)
+        vis.embeddingsBuffer.write(big)
+        assert np.array_equal(vis.render(), oracle.heatmap(big))
+        vis.destroy()
+    finally:
+        gpt.destroy()
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_load_from_weight_folder(tmp_path, fused):
+    """GPT(folder) reads the reference's directory format and computes what GPT(weights=...) computes."""
+    from webgpt_b200 import GPT
+    params = synth.CONFIGS["tiny"]
+    w = synth.make_weights(params, seed=8, std=0.2, ln_random=True)
+    folder = str(tmp_path / "m")
+    synth.write_weight_folder(folder, params, w)
+    a = GPT(folder, fused=fused)
+    a.initialize()
+    b = make_gpt(params, w, fused)
+    try:
+        ids = synth.make_tokens(params["vocab_size"], 9, seed=2)
+        assert np.array_equal(a.run(ids), b.run(ids))
+    finally:
+        a.destroy()
+        b.destroy()

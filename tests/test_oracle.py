@@ -166,3 +166,18 @@ def test_model_rejects_bad_params(oracle):
     params = dict(synth.CONFIGS["tiny"], n_head=3)  # n_embd % n_head != 0, model.js:295
     with pytest.raises(ValueError):
         oracle.Model(params, [np.zeros(1, np.float32)] * (4 + 12 * params["n_layer"]))
+
+
+def test_heatmap_known_values(oracle):
+    """visuals.js:104-135 on hand-computed pixels."""
+    v = np.array([0.0, 5.0, -5.0, 10.0, 15.0, -15.0, 17.0, -30.0, 1e9], np.float32)
+    px = oracle.heatmap(v)
+    assert px[0].tolist() == [0, 0, 0, 0]
+    assert px[1].tolist() == [128, 0, 0, 0]      # 0.5 -> 127.5 -> rounds to 128
+    assert px[2].tolist() == [0, 0, 128, 0]
+    assert px[3].tolist() == [255, 0, 0, 0]      # exactly the threshold: no green yet
+    assert px[4].tolist() == [255, 128, 0, 0]    # 1.5: green = 0.5
+    assert px[5].tolist() == [0, 128, 255, 0]
+    assert px[6].tolist() == [255, 179, 0, 0]    # green capped at 0.7 -> 178.5 -> 179
+    assert px[7].tolist() == [0, 179, 255, 0]
+    assert px[8].tolist() == [255, 179, 0, 0]

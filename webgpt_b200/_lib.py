@@ -82,6 +82,7 @@ SIGNATURES = {
     "wgpt_session_set_prompts": [vp, vp, i32],
     "wgpt_session_generate": [vp, i32],
     "wgpt_session_get_new_ids": [vp, i32, vp],
+    "wgpt_visuals_render": [vp, vp, i32, i32, vp],
     "wgpt_session_tap": [vp, vp, u64, C.POINTER(u64)],
 }
 _SPECIAL = {"wgpt_abi_version": (i32, []), "wgpt_last_error": (C.c_char_p, [])}

@@ -747,6 +747,17 @@ WGPT_EXPORT int32_t wgpt_softmax(wgpt_device *dev, int32_t rows, int32_t cols, c
   return WGPT_OK;
 }
 
+WGPT_EXPORT int32_t wgpt_visuals_render(wgpt_device *dev, const float *embeddings, int32_t n_ctx, int32_t n_embd,
+                                        uint8_t *rgba_out) {
+  TRY(use(dev));
+  REQUIRE(embeddings && rgba_out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(n_ctx >= 1 && n_embd >= 1, WGPT_ERR_SHAPE, "empty image %dx%d", n_embd, n_ctx);
+  REQUIRE((reinterpret_cast<uintptr_t>(rgba_out) & 3u) == 0, WGPT_ERR_ALIGN, "rgba_out must be 4-byte aligned");
+  size_t n = (size_t)n_ctx * n_embd;
+  LAUNCH(dev, heatmap_kernel, grid_for(n, 256, dev->sm_count), 256, 0, embeddings, reinterpret_cast<uchar4 *>(rgba_out), n);
+  return WGPT_OK;
+}
+
 static int32_t check_err_word(wgpt_device *dev, const char *what) {
   int h = 0;
   CK(cudaMemcpyAsync(&h, dev->d_err, sizeof h, cudaMemcpyDeviceToHost, dev->stream));

@@ -185,4 +185,32 @@ __global__ void transpose_kernel(const float *__restrict__ in, float *__restrict
   }
 }
 
+
+// Heat map of the residual stream, the fragment shader of the reference's visualiser (visuals.js:104-135) run
+// headless: pixel (x, y) of an n_embd x n_ctx image shows v = 0.1 * buf[y*n_embd + x]; negative values go to
+// blue (plus green beyond -1), positive to red (plus green beyond +1), green capped at 0.7, alpha left at 0 as
+// in the shader. Output is RGBA8 (unorm: clamp to [0,1], round to nearest), 4 bytes per pixel, row-major.
+__global__ void heatmap_kernel(const float *__restrict__ buf, uchar4 *__restrict__ rgba, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v = buf[i] * 0.1f;
+    float r = 0.f, g = 0.f, b = 0.f;
+    if (v < 0.f) {
+      b = -v;
+      if (v < -1.0f) g = -v - 1.0f;
+    } else {
+      r = v;
+      if (v > 1.0f) g = v - 1.0f;
+    }
+    g = fminf(g, 0.7f);
+    uchar4 px;
+    px.x = (unsigned char)floorf(fminf(fmaxf(r, 0.f), 1.f) * 255.f + 0.5f);
+    px.y = (unsigned char)floorf(fminf(fmaxf(g, 0.f), 1.f) * 255.f + 0.5f);
+    px.z = (unsigned char)floorf(fminf(fmaxf(b, 0.f), 1.f) * 255.f + 0.5f);
+    px.w = 0;
+    rgba[i] = px;
+  }
+}
+
 }  // namespace wgpt

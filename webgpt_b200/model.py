@@ -265,6 +265,10 @@ class GPT:
         else:
             with open(os.path.join(weightsFolder, "params_gpt.json")) as f:
                 params = json.load(f)
+            # the exporters write the HF config (n_positions beside or instead of n_ctx) or nanoGPT's model args
+            # (block_size, as condensed/condensed.js:1726 reads it)
+            if "n_ctx" not in params:
+                params["n_ctx"] = params.get("n_positions", params.get("block_size"))
         if params["n_embd"] % 4 != 0:
             raise ValueError("Model load failed: n_embd must be divisible by 4.")
         if params["n_embd"] % params["n_head"] != 0:

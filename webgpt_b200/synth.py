@@ -91,3 +91,16 @@ def make_int8_case(M, K, N, seed=11):
     scales = rng.uniform(0.001, 0.02, size=N).astype(np.float32)
     A = rng.standard_normal((M, K), dtype=np.float32)
     return A, q, packed, scales
+
+
+def write_weight_folder(path, params, weights):
+    """Writes a weight directory in the reference's on-disk format: params_gpt.json plus one raw little-endian
+    f32 file "<state-dict key>_gpt.bin" per tensor (other/conversion_scripts/convert_pretrained_pytorch.py:19-42;
+    read back by model.js:289-291, 341, 371, 379-383, 405-420)."""
+    import json
+    import os
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "params_gpt.json"), "w") as f:
+        json.dump({k: params[k] for k in ("n_layer", "n_head", "n_embd", "n_ctx", "vocab_size")}, f, indent=4)
+    for name in tensor_names(params):
+        np.ascontiguousarray(weights[name], dtype="<f4").tofile(os.path.join(path, f"{name}_gpt.bin"))
