@@ -853,6 +853,14 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
   Epilogue e = plain_epi(out, N, nullptr);
   e.colscale = scale;
   if (M > 16) {
+    if (dev->precision != WGPT_PRECISION_FP32) {
+      // expand the words to an FP32 [N,K] weight in scratch, then the tcgen05 GEMM with the scales in its epilogue
+      TRY(scratch_reserve(dev, (size_t)N * K * 4));
+      float *wt = static_cast<float *>(dev->scratch);
+      dim3 xgrid((N / 4 + 31) / 32, (K + 31) / 32);
+      LAUNCH(dev, int8_expand_nk_kernel, xgrid, 256, 0, Bq, K, N, wt);
+      return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e);
+    }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     LAUNCH(dev, int8_gemm_simt_kernel, grid, 256, 0, A, Bq, M, K, N, e);
     return WGPT_OK;
@@ -1107,6 +1115,10 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   // position slices per (sequence, head): a cluster of 1, 2, 4 or 8 CTAs, enough to put about two CTAs on every SM
   int split = 1;
   while (split < 8 && p.n_head * n_seq * split * 2 <= 2 * m->dev->sm_count) split *= 2;
+  if (const char *ev = getenv("WGPT_ATTN_SPLIT")) {  // tuning override: 1, 2, 4 or 8
+    int v = atoi(ev);
+    if (v == 1 || v == 2 || v == 4 || v == 8) split = v;
+  }
   s->n_split = split;
   cudaError_t e = cudaMalloc(&s->kc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->vc, kv * 4);

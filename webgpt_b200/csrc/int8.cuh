@@ -129,4 +129,27 @@ int8_gemm_simt_kernel(const float *__restrict__ A, const uint32_t *__restrict__ 
   }
 }
 
+// Large M on the tensor cores: the packed words are expanded once per call to an FP32 weight in the [N,K] layout
+// the tcgen05 GEMM reads (K contiguous). The integers are exact in TF32, so the product keeps the accuracy of the
+// activation split alone. 32 k x 128 columns per CTA, transposed through shared memory so that both the word reads
+// (along N) and the float writes (along K) are coalesced.
+__global__ void __launch_bounds__(256)
+int8_expand_nk_kernel(const uint32_t *__restrict__ Bq, int K, int N, float *__restrict__ Wt) {
+  __shared__ float t[32][129];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int k0 = blockIdx.y * 32, w0 = blockIdx.x * 32, ND4 = N >> 2;
+#pragma unroll
+  for (int r = 0; r < 4; r++) {
+    int k = warp + 8 * r;
+    float f[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 + k < K && w0 + lane < ND4) unpack_int8x4(__ldg(Bq + (size_t)(k0 + k) * ND4 + w0 + lane), f);
+    t[k][4 * lane + 0] = f[0]; t[k][4 * lane + 1] = f[1]; t[k][4 * lane + 2] = f[2]; t[k][4 * lane + 3] = f[3];
+  }
+  __syncthreads();
+  for (int i = warp; i < 128; i += 8) {
+    int n = w0 * 4 + i;
+    if (n < N && k0 + lane < K) Wt[(size_t)n * K + k0 + lane] = t[lane][i];
+  }
+}
+
 }  // namespace wgpt
