@@ -230,6 +230,27 @@ int32_t wgpt_session_set_prompts(wgpt_session *session, const uint32_t *prompts_
 int32_t wgpt_session_generate(wgpt_session *session, int32_t n_new);
 int32_t wgpt_session_get_new_ids(wgpt_session *session, int32_t n_new, uint32_t *new_ids_host);
 
+/* GPT.generate with top_k > 1 (model.js:53-102): after each forward pass the reference reads the logits back
+ * and runs selectTopK -> cpuSoftmax(temperature) -> sampleFromDistribution on the CPU (model.js:81-83,
+ * globals.js:47-74). Here that chain runs on the device between decode steps, so nothing is read back per token.
+ * The reference draws Math.random() inside sampleFromDistribution (globals.js:48); these calls take the uniform
+ * numbers from the caller instead: uniforms_host is [n_new, n_seq] doubles in [0,1), number [i, q] deciding token
+ * i of sequence q. Same arithmetic as the reference: stable descending order (lowest index first among equal
+ * logits), exp((v - max) / temperature) in double precision, left-to-right sums, first index whose running sum
+ * exceeds the uniform number, else the last. top_k is limited to WGPT_MAX_TOP_K (the reference's page allows
+ * 1..100). wgpt_session_generate_sample is the enqueue-only stage, like wgpt_session_generate. */
+#define WGPT_MAX_TOP_K 128
+int32_t wgpt_generate_sample(wgpt_session *session, const uint32_t *prompts_host, int32_t n_prompt, int32_t n_new,
+                             int32_t top_k, double temperature, const double *uniforms_host,
+                             uint32_t *new_ids_host);
+int32_t wgpt_session_generate_sample(wgpt_session *session, int32_t n_new, int32_t top_k, double temperature,
+                                     const double *uniforms_host);
+
+/* The sampling step alone, on device buffers: one pick per row of logits [n_rows, V] with uniforms [n_rows]
+ * (doubles) into ids_out [n_rows] (globals.js:47-74 as above). */
+int32_t wgpt_sample_topk(wgpt_device *dev, const float *logits, int32_t n_rows, int32_t V, int32_t top_k,
+                         double temperature, const double *uniforms, uint32_t *ids_out);
+
 /* GPT.externalBuffer tap (model.js:18,211-222): copies the residual stream before ln_f of the most recent
  * forward ([rows, n_embd], rows = n_seq * tokens of that call) into dst (device memory). */
 int32_t wgpt_session_tap(wgpt_session *session, float *dst, uint64_t max_floats, uint64_t *floats_written);

@@ -508,6 +508,82 @@ ORC_API int orc_kv_generate_greedy(orc_kv *s, const uint32_t *prompt, int n_prom
   return 0;
 }
 
+/* ------------------------------------------------- top-k sampling ---- */
+/* One sampling step of GPT.generate, model.js:81-83, with the uniform random number supplied by the caller
+ * (the reference draws Math.random() inside sampleFromDistribution, globals.js:48):
+ *   selectTopK (globals.js:66-74): indices sorted by descending logit with a stable sort, so equal values keep
+ *     ascending index order (-0 and +0 compare equal there); the first top_k are kept;
+ *   cpuSoftmax (globals.js:59-64): exp((v - max) / temperature) in double precision, summed left to right;
+ *   sampleFromDistribution (globals.js:47-57): the first i whose running sum exceeds u, else the last.
+ * Returns the chosen vocabulary index; the selected indices are written to top_idx (top_k entries) when not NULL. */
+ORC_API uint32_t orc_sample_topk(const float *logits, int V, int top_k, double temperature, double u,
+                                 uint32_t *top_idx) {
+  if (top_k > V) top_k = V;
+  if (top_k < 1) top_k = 1;
+  uint32_t *sel = malloc((size_t)top_k * 4);
+  /* insertion into a descending list; a later index never displaces an equal earlier one */
+  int n = 0;
+  for (int v = 0; v < V; v++) {
+    float x = logits[v];
+    if (n == top_k && !(x > logits[sel[n - 1]])) continue;
+    int j = n < top_k ? n : top_k - 1;
+    while (j > 0 && x > logits[sel[j - 1]]) { sel[j] = sel[j - 1]; j--; }
+    sel[j] = (uint32_t)v;
+    if (n < top_k) n++;
+  }
+  double *e = malloc((size_t)top_k * sizeof(double));
+  double maxv = (double)logits[sel[0]];
+  for (int j = 1; j < top_k; j++) if ((double)logits[sel[j]] > maxv) maxv = (double)logits[sel[j]];
+  double sum = 0.0;
+  for (int j = 0; j < top_k; j++) { e[j] = exp(((double)logits[sel[j]] - maxv) / temperature); sum += e[j]; }
+  int pick = top_k - 1;
+  double cum = 0.0;
+  for (int j = 0; j < top_k; j++) {
+    cum += e[j] / sum;
+    if (u < cum) { pick = j; break; }
+  }
+  uint32_t id = sel[pick];
+  if (top_idx) memcpy(top_idx, sel, (size_t)top_k * 4);
+  free(e);
+  free(sel);
+  return id;
+}
+
+/* Sampled generation through the KV cache: like orc_kv_generate_greedy with orc_sample_topk as the pick;
+ * uniforms holds one number per new token. Requires n_prompt + n_new <= n_ctx. */
+ORC_API int orc_kv_generate_sample(orc_kv *s, const uint32_t *prompt, int n_prompt, int n_new, int top_k,
+                                   double temperature, const double *uniforms, uint32_t *new_ids) {
+  int V = s->m->vocab;
+  if (n_prompt + n_new > s->m->n_ctx) return -1;
+  float *logits = malloc((size_t)V * 4);
+  orc_kv_reset(s);
+  for (int i = 0; i < n_prompt; i++)
+    if (orc_kv_step(s, prompt[i], i == n_prompt - 1 ? logits : NULL)) { free(logits); return -2; }
+  for (int i = 0; i < n_new; i++) {
+    new_ids[i] = orc_sample_topk(logits, V, top_k, temperature, uniforms[i], NULL);
+    if (i + 1 < n_new && orc_kv_step(s, new_ids[i], logits)) { free(logits); return -3; }
+  }
+  free(logits);
+  return 0;
+}
+
+/* Sampled generation by full-window recompute, the reference's own loop (model.js:53-102). */
+ORC_API int orc_generate_sample(const orc_model *m, const uint32_t *prompt, int n_prompt, int n_new, int top_k,
+                                double temperature, const double *uniforms, uint32_t *history_out) {
+  int V = m->vocab;
+  float *logits = malloc((size_t)V * 4);
+  memcpy(history_out, prompt, (size_t)n_prompt * 4);
+  int len = n_prompt;
+  for (int i = 0; i < n_new; i++) {
+    int T = len < m->n_ctx ? len : m->n_ctx;
+    int rc = orc_model_run(m, history_out + (len - T), T, logits, NULL);
+    if (rc) { free(logits); return rc; }
+    history_out[len++] = orc_sample_topk(logits, V, top_k, temperature, uniforms[i], NULL);
+  }
+  free(logits);
+  return 0;
+}
+
 /* Visualiser fragment shader, visuals.js:104-135: pixel (x,y) reads buf[y*n_embd + x] (the canvas is n_embd x
  * n_ctx pixels and fragCoord is the pixel centre, :105-110), v = 0.1*value (:115); hdrColorMapping with threshold 1
  * (:120-135): v<0 -> b=-v, and g=-v-1 below -1; else r=v, and g=v-1 above 1; g=min(g,0.7). The vec4 starts at

@@ -62,6 +62,11 @@ def lib():
         L.orc_kv_reset.argtypes = [C.c_void_p]
         L.orc_kv_step.argtypes = [C.c_void_p, C.c_uint32, f32p]
         L.orc_kv_generate_greedy.argtypes = [C.c_void_p, u32p, C.c_int, C.c_int, u32p]
+        f64p = C.POINTER(C.c_double)
+        L.orc_sample_topk.restype = C.c_uint32
+        L.orc_sample_topk.argtypes = [f32p, C.c_int, C.c_int, C.c_double, C.c_double, u32p]
+        L.orc_kv_generate_sample.argtypes = [C.c_void_p, u32p, C.c_int, C.c_int, C.c_int, C.c_double, f64p, u32p]
+        L.orc_generate_sample.argtypes = [C.c_void_p, u32p, C.c_int, C.c_int, C.c_int, C.c_double, f64p, u32p]
         L.orc_int8_quantize.argtypes = [f32p, C.c_size_t, C.c_double, i32p]
         L.orc_int8_unpack.argtypes = [i32p, C.c_size_t, C.POINTER(C.c_int8)]
     return _LIB
@@ -201,6 +206,15 @@ def int8_matmul(A, Bq, scale, N, literal=False):
     return out
 
 
+def sample_topk(logits, top_k, temperature, u, return_top=False):
+    """model.js:81-83 with the random number supplied: returns the sampled vocabulary index."""
+    logits, pl = _f(logits)
+    k = min(int(top_k), logits.size)
+    top = np.empty(k, np.uint32)
+    idx = lib().orc_sample_topk(pl, logits.size, int(top_k), float(temperature), float(u), top.ctypes.data_as(u32p))
+    return (int(idx), top) if return_top else int(idx)
+
+
 def heatmap(buf):
     buf, pb = _f(buf)
     out = np.empty(buf.shape + (4,), np.uint8)
@@ -264,6 +278,32 @@ class Model:
         if rc:
             raise ValueError(f"orc_kv_generate_greedy failed: {rc}")
         return out
+
+    def kv_generate_sample(self, prompt, n_new, top_k, temperature, uniforms):
+        """Top-k sampling through the KV cache; uniforms holds one number in [0,1) per new token."""
+        prompt, pp = _u(prompt)
+        u = np.ascontiguousarray(uniforms, dtype=np.float64)
+        assert len(u) >= n_new
+        kv = lib().orc_kv_create(self._h)
+        out = np.empty(n_new, np.uint32)
+        rc = lib().orc_kv_generate_sample(kv, pp, len(prompt), n_new, top_k, float(temperature),
+                                          u.ctypes.data_as(C.POINTER(C.c_double)), out.ctypes.data_as(u32p))
+        lib().orc_kv_destroy(kv)
+        if rc:
+            raise ValueError(f"orc_kv_generate_sample failed: {rc}")
+        return out
+
+    def generate_sample(self, prompt, n_new, top_k, temperature, uniforms):
+        """Top-k sampling by full-window recompute (the reference's loop); returns prompt + new ids."""
+        prompt, pp = _u(prompt)
+        u = np.ascontiguousarray(uniforms, dtype=np.float64)
+        assert len(u) >= n_new
+        hist = np.empty(len(prompt) + n_new, np.uint32)
+        rc = lib().orc_generate_sample(self._h, pp, len(prompt), n_new, top_k, float(temperature),
+                                       u.ctypes.data_as(C.POINTER(C.c_double)), hist.ctypes.data_as(u32p))
+        if rc:
+            raise ValueError(f"orc_generate_sample failed: {rc}")
+        return hist
 
     def kv_logits(self, ids):
         """Feeds ids one by one through the KV cache; returns the logits after each."""

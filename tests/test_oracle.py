@@ -181,3 +181,49 @@ def test_heatmap_known_values(oracle):
     assert px[6].tolist() == [255, 179, 0, 0]    # green capped at 0.7 -> 178.5 -> 179
     assert px[7].tolist() == [0, 179, 255, 0]
     assert px[8].tolist() == [255, 179, 0, 0]
+
+
+def _sample_cases():
+    rng = np.random.default_rng(77)
+    cases = []
+    for V in (5, 257, 1000, 50257):
+        cases.append(rng.standard_normal(V).astype(np.float32) * 4 - 30)           # distinct values
+        cases.append(np.round(rng.standard_normal(V) * 2).astype(np.float32))      # many exact ties, +0 and -0
+    z = np.zeros(64, np.float32)
+    z[1::2] = -0.0
+    cases.append(z)                                                                 # all equal under JS ordering
+    return cases
+
+
+def test_sample_topk_matches_host_mirror(oracle):
+    """The C restatement of model.js:81-83 against the Python mirror of the same three helpers
+    (globals.js:47-74), written independently: same kept indices in the same order, same pick."""
+    from webgpt_b200 import globals as G
+    rng = np.random.default_rng(5)
+    for logits in _sample_cases():
+        for top_k in (1, 2, 3, 40, 100):
+            for temperature in (0.1, 0.7, 1.0, 2.0):
+                for u in (0.0, float(rng.random()), float(rng.random()), 0.9999999999):
+                    got, top = oracle.sample_topk(logits, top_k, temperature, u, return_top=True)
+                    sel = G.selectTopK(logits, top_k)
+                    assert [int(t) for t in top] == sel["topKIndices"]
+                    probs = G.cpuSoftmax(sel["topKProbs"], temperature)
+                    assert got == sel["topKIndices"][G.sampleFromDistribution(probs, u)]
+    # top_k = 1 is the greedy pick
+    x = _sample_cases()[1]
+    assert oracle.sample_topk(x, 1, 1.0, 0.5) == int(oracle.lib().orc_argmax(oracle._f(x)[1], x.size))
+
+
+def test_sampled_generation_kv_equals_recompute(oracle):
+    params = synth.CONFIGS["tiny"]
+    w = synth.make_weights(params, seed=3, std=0.15, ln_random=True)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    prompt = synth.make_tokens(params["vocab_size"], 5, seed=1)
+    n_new = params["n_ctx"] - 5
+    u = np.random.default_rng(8).random(n_new)
+    a = m.kv_generate_sample(prompt, n_new, 3, 0.8, u)
+    b = m.generate_sample(prompt, n_new, 3, 0.8, u)
+    assert np.array_equal(a, b[5:])
+    assert len(set(int(t) for t in a)) > 1
+    # top_k = 1 ignores the random numbers and equals the greedy loop
+    assert np.array_equal(m.kv_generate_sample(prompt, n_new, 1, 0.8, u), m.kv_generate_greedy(prompt, n_new))

@@ -13,6 +13,7 @@ OK = 0
 ERR_SHAPE, ERR_ALIGN, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_STATE, ERR_UNSUPPORTED, ERR_ARG = -1, -2, -3, -4, -5, -6, -7, -8
 PRECISION_FP32, PRECISION_TF32X3, PRECISION_TF32 = 0, 1, 2
 
+MAX_TOP_K = 128  # WGPT_MAX_TOP_K
 _ERR_NAMES = {ERR_SHAPE: "WGPT_ERR_SHAPE", ERR_ALIGN: "WGPT_ERR_ALIGN", ERR_OOM: "WGPT_ERR_OOM",
               ERR_CUDA: "WGPT_ERR_CUDA", ERR_TIMEOUT: "WGPT_ERR_TIMEOUT", ERR_STATE: "WGPT_ERR_STATE",
               ERR_UNSUPPORTED: "WGPT_ERR_UNSUPPORTED", ERR_ARG: "WGPT_ERR_ARG"}
@@ -82,6 +83,9 @@ SIGNATURES = {
     "wgpt_session_set_prompts": [vp, vp, i32],
     "wgpt_session_generate": [vp, i32],
     "wgpt_session_get_new_ids": [vp, i32, vp],
+    "wgpt_generate_sample": [vp, vp, i32, i32, i32, C.c_double, vp, vp],
+    "wgpt_session_generate_sample": [vp, i32, i32, C.c_double, vp],
+    "wgpt_sample_topk": [vp, vp, i32, i32, i32, C.c_double, vp, vp],
     "wgpt_visuals_render": [vp, vp, i32, i32, vp],
     "wgpt_session_tap": [vp, vp, u64, C.POINTER(u64)],
 }

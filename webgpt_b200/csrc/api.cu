@@ -19,6 +19,7 @@
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
 #include "int8.cuh"
+#include "sampling.cuh"
 #include "matmul.cuh"
 
 using namespace wgpt;
@@ -1074,6 +1075,11 @@ struct wgpt_session {
   int *pk_cand_idx;
   unsigned long long *pk_counter;
   int *pk_abort;
+  // top-k sampling (0 = greedy pick): parameters and the per-(step, sequence) uniform numbers on the device
+  int sample_k = 0;
+  double sample_temp = 1.0;
+  double *d_uniform = nullptr;
+  size_t uniform_cap = 0;  // doubles
   cudaGraphExec_t step_graph;  // one captured decode step (pointers of this session baked in)
   uint64_t step_graph_launches;
   bool step_warm;
@@ -1152,6 +1158,7 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   cudaFree(s->pk_cand_val); cudaFree(s->pk_cand_idx); cudaFree(s->pk_counter); cudaFree(s->pk_abort);
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
   cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
+  cudaFree(s->d_uniform);
   delete s;
   return WGPT_OK;
 }
@@ -1254,12 +1261,13 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   s->last_rows = M;
   if (gemv_nk_fits(dev, s->n_seq, E)) {
     GreedyPick gp = no_pick();
-    if (pick) {  // arg-max and position advance ride on the de-embedding kernel
+    if (pick && s->sample_k == 0) {  // arg-max and position advance ride on the de-embedding kernel
       gp.pval = s->pick_val; gp.pidx = s->pick_idx; gp.counter = s->attn_cnt + (size_t)s->n_seq * H;
       gp.next_ids = s->next_ids; gp.out_ids = s->out_ids; gp.out_stride = s->out_cap;
       gp.pos = s->d_pos; gp.step = s->d_step; gp.n_tok = n_tok;
     }
     TRY(launch_gemv_nk(dev, s->n_seq, x_last, ld_last, m->lnf_g, m->lnf_b, m->wte, E, p.vocab_size, e, gp));
+    if (pick && s->sample_k > 0) return pick_and_advance(s, n_tok);
     if (pick) s->len += n_tok;
     return WGPT_OK;
   }
@@ -1321,7 +1329,29 @@ static int32_t reserve_out_ids(wgpt_session *s, int n_new) {
 
 // Arg-max of the newest logits of every sequence -> next input ids and output list; the same kernel then advances
 // the session's position by n_tok and its step counter by one.
+static int32_t launch_sample_topk(wgpt_device *dev, const float *logits, int n_rows, int V, int top_k,
+                                  double temperature, const double *uniforms, uint32_t *next_ids, uint32_t *out_ids,
+                                  int out_stride, int *pos, int *step, int n_tok, unsigned int *counter) {
+  const int per_thread = (V + kSampleThreads - 1) / kSampleThreads;
+  const size_t cap = (size_t)top_k * per_thread;
+  const size_t smem = (kSampleThreads + cap) * sizeof(unsigned long long);
+  REQUIRE(smem <= size_t(200) << 10, WGPT_ERR_SHAPE,
+          "top_k %d with a vocabulary of %d needs %zu bytes of shared memory for the candidate list", top_k, V, smem);
+  if (smem > 40 * 1024)  // the kernel's static arrays count against the 48 KB default as well
+    CK(cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LAUNCH_PDL(dev, sample_topk_kernel, n_rows, kSampleThreads, smem, logits, V, top_k, temperature, uniforms, (int)cap,
+             next_ids, out_ids, out_stride, pos, step, n_tok, counter);
+  return WGPT_OK;
+}
+
 static int32_t pick_and_advance(wgpt_session *s, int n_tok) {
+  if (s->sample_k > 0) {
+    TRY(launch_sample_topk(s->m->dev, s->logits, s->n_seq, s->m->p.vocab_size, s->sample_k, s->sample_temp,
+                           s->d_uniform, s->next_ids, s->out_ids, s->out_cap, s->d_pos, s->d_step, n_tok,
+                           s->attn_cnt + (size_t)s->n_seq * s->m->p.n_head));
+    s->len += n_tok;
+    return WGPT_OK;
+  }
   LAUNCH_PDL(s->m->dev, argmax_kernel, s->n_seq, 1024, 0, (const float *)s->logits, s->m->p.vocab_size, s->next_ids,
              s->out_ids, s->out_cap, s->d_pos, s->d_step, n_tok, s->attn_cnt + (size_t)s->n_seq * s->m->p.n_head);
   s->len += n_tok;
@@ -1489,10 +1519,50 @@ WGPT_EXPORT int32_t wgpt_session_set_prompts(wgpt_session *s, const uint32_t *pr
   return set_prompts(s, prompts_host, n_prompt);
 }
 
+// Switches the session between the greedy pick (top_k = 0) and top-k sampling; the captured decode step holds
+// the pick kernel and its arguments, so a change drops it.
+static void set_pick_mode(wgpt_session *s, int top_k, double temperature) {
+  if (s->sample_k != top_k || (top_k > 0 && s->sample_temp != temperature)) drop_step_graph(s);
+  s->sample_k = top_k;
+  s->sample_temp = temperature;
+}
+
+static int32_t generate(wgpt_session *s, int32_t n_new);
+
 WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
   REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
+  TRY(use(s->m->dev));
+  set_pick_mode(s, 0, 1.0);
+  return generate(s, n_new);
+}
+
+WGPT_EXPORT int32_t wgpt_session_generate_sample(wgpt_session *s, int32_t n_new, int32_t top_k, double temperature,
+                                                 const double *uniforms_host) {
+  REQUIRE(s && uniforms_host, WGPT_ERR_ARG, "null argument");
   wgpt_device *dev = s->m->dev;
   TRY(use(dev));
+  REQUIRE(n_new >= 1, WGPT_ERR_SHAPE, "n_new must be at least 1");
+  REQUIRE(top_k >= 1 && top_k <= kMaxTopK && top_k <= s->m->p.vocab_size, WGPT_ERR_SHAPE,
+          "top_k %d outside 1..%d", top_k, kMaxTopK < s->m->p.vocab_size ? kMaxTopK : s->m->p.vocab_size);
+  REQUIRE(temperature > 0.0, WGPT_ERR_ARG, "temperature must be positive");
+  size_t n_u = (size_t)n_new * s->n_seq;
+  if (n_u > s->uniform_cap) {
+    CK(cudaStreamSynchronize(dev->stream));
+    drop_step_graph(s);  // the captured step holds the old address
+    cudaFree(s->d_uniform);
+    s->d_uniform = nullptr;
+    s->uniform_cap = 0;
+    CK(cudaMalloc(&s->d_uniform, n_u * sizeof(double)));
+    s->uniform_cap = n_u;
+  }
+  CK(cudaMemcpyAsync(s->d_uniform, uniforms_host, n_u * sizeof(double), cudaMemcpyHostToDevice, dev->stream));
+  CK(cudaStreamSynchronize(dev->stream));  // uniforms_host may be pageable and is the caller's again on return
+  set_pick_mode(s, top_k, temperature);
+  return generate(s, n_new);
+}
+
+static int32_t generate(wgpt_session *s, int32_t n_new) {
+  wgpt_device *dev = s->m->dev;
   const int n_ctx = s->m->p.n_ctx, n_seq = s->n_seq, n_prompt = s->n_prompt;
   REQUIRE(n_prompt >= 1, WGPT_ERR_STATE, "no prompts set");
   REQUIRE(n_new >= 1, WGPT_ERR_SHAPE, "n_new must be at least 1");
@@ -1511,7 +1581,7 @@ WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
   TRY(forward(s, s->ids, first, true));
   TRY(pk_prepare(s));
   int i_start = 1;
-  if (s->pk_ok && n_new > 1) {
+  if (s->pk_ok && n_new > 1 && s->sample_k == 0) {
     // all remaining steps that fit in the context window run inside one persistent kernel
     int fit = n_ctx - s->len;
     int run = n_new - 1 < fit ? n_new - 1 : fit;
@@ -1570,6 +1640,34 @@ WGPT_EXPORT int32_t wgpt_generate_greedy(wgpt_session *s, const uint32_t *prompt
   TRY(set_prompts(s, prompts_host, n_prompt));
   TRY(wgpt_session_generate(s, n_new));
   return wgpt_session_get_new_ids(s, n_new, new_ids_host);
+}
+
+WGPT_EXPORT int32_t wgpt_generate_sample(wgpt_session *s, const uint32_t *prompts_host, int32_t n_prompt,
+                                         int32_t n_new, int32_t top_k, double temperature,
+                                         const double *uniforms_host, uint32_t *new_ids_host) {
+  REQUIRE(s && prompts_host && new_ids_host && uniforms_host, WGPT_ERR_ARG, "null argument");
+  TRY(use(s->m->dev));
+  REQUIRE(n_prompt >= 1 && n_new >= 1, WGPT_ERR_SHAPE, "n_prompt and n_new must be at least 1");
+  TRY(set_prompts(s, prompts_host, n_prompt));
+  TRY(wgpt_session_generate_sample(s, n_new, top_k, temperature, uniforms_host));
+  return wgpt_session_get_new_ids(s, n_new, new_ids_host);
+}
+
+// Per-operator form of the sampling step: one pick per row of logits[n_rows, V] (all device pointers).
+WGPT_EXPORT int32_t wgpt_sample_topk(wgpt_device *dev, const float *logits, int32_t n_rows, int32_t V, int32_t top_k,
+                                     double temperature, const double *uniforms, uint32_t *ids_out) {
+  TRY(use(dev));
+  REQUIRE(logits && uniforms && ids_out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(n_rows >= 1 && V >= 1, WGPT_ERR_SHAPE, "empty logits");
+  REQUIRE(top_k >= 1 && top_k <= kMaxTopK && top_k <= V, WGPT_ERR_SHAPE, "top_k %d outside 1..%d", top_k,
+          kMaxTopK < V ? kMaxTopK : V);
+  REQUIRE(temperature > 0.0, WGPT_ERR_ARG, "temperature must be positive");
+  // position, step and done counters of the kernel's advance step live in the workspace, zeroed per call
+  TRY(scratch_reserve(dev, 256));
+  int *ctr = static_cast<int *>(dev->scratch);
+  CK(cudaMemsetAsync(ctr, 0, 16, dev->stream));
+  return launch_sample_topk(dev, logits, n_rows, V, top_k, temperature, uniforms, ids_out, nullptr, 0, ctr, ctr + 1, 1,
+                            reinterpret_cast<unsigned int *>(ctr + 2));
 }
 
 WGPT_EXPORT int32_t wgpt_session_tap(wgpt_session *s, float *dst, uint64_t max_floats, uint64_t *floats_written) {

@@ -1,8 +1,9 @@
 """class GPT with the surface of the reference's model.js, driving the B200 kernels through the C ABI.
 
 Two execution routes share one weight source:
-  * the fused route (default): weights live in a `wgpt_model`, `run` is one `wgpt_model_run` call and greedy
-    `generate` is one `wgpt_generate_greedy` call with the KV cache and the arg-max on the device;
+  * the fused route (default): weights live in a `wgpt_model`, `run` is one `wgpt_model_run` call and
+    `generate` is one `wgpt_generate_greedy` (top_k = 1) or `wgpt_generate_sample` call with the KV cache and
+    the pick on the device;
   * the pass-list route (`fused=False`): `run` builds the reference's pass list from the instruction classes
     (model.js:114-241) and replays it (model.js:245-257), one C-ABI call per operator.
 Token ids go in and come out as integers; the reference's tokenizers (tokenizer.js) are host-side string code
@@ -13,6 +14,7 @@ import ctypes as C
 import json
 import math
 import os
+import random
 import time
 
 import numpy as np
@@ -51,6 +53,15 @@ class Session:
         prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.n_seq, -1)
         out = np.empty((self.n_seq, n_new), np.uint32)
         _lib.call("wgpt_generate_greedy", self.handle, prompts.ctypes.data, prompts.shape[1], n_new, out.ctypes.data)
+        return out
+
+    def generate_sample(self, prompts, n_new, top_k, temperature, uniforms):
+        """Top-k sampling on the device (model.js:81-83); uniforms is [n_new, n_seq] numbers in [0,1)."""
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint32).reshape(self.n_seq, -1)
+        u = np.ascontiguousarray(uniforms, dtype=np.float64).reshape(n_new, self.n_seq)
+        out = np.empty((self.n_seq, n_new), np.uint32)
+        _lib.call("wgpt_generate_sample", self.handle, prompts.ctypes.data, prompts.shape[1], n_new, int(top_k),
+                  float(temperature), u.ctypes.data, out.ctypes.data)
         return out
 
     def tap(self):
@@ -136,6 +147,17 @@ class GPT:
             # Greedy: one call; KV cache, arg-max and window handling are inside the library.
             t0 = time.perf_counter()
             new = self.session().generate_greedy(np.array(history, np.uint32), max_new_tokens)[0]
+            self.averageKernelTime = (time.perf_counter() - t0) * 1e3 / max_new_tokens
+            for t in new:
+                yield dec(int(t))
+            return
+        top_k, temperature = int(top_k), float(temperature)  # the page passes both as strings (index.html:89-91)
+        if self._fused and top_k <= _lib.MAX_TOP_K:
+            # Sampled: also one call. The random numbers are drawn here, one per token in order as
+            # sampleFromDistribution would draw them (globals.js:48), and the picks happen on the device.
+            u = np.array([(rand() if rand else random.random()) for _ in range(max_new_tokens)], np.float64)
+            t0 = time.perf_counter()
+            new = self.session().generate_sample(np.array(history, np.uint32), max_new_tokens, top_k, temperature, u)[0]
             self.averageKernelTime = (time.perf_counter() - t0) * 1e3 / max_new_tokens
             for t in new:
                 yield dec(int(t))
