@@ -66,6 +66,36 @@ def test_gemm_tc_index_pattern(dev):
         assert np.array_equal(run_nk(dev, A, Wt, b, mode).astype(np.float64), ref)
 
 
+@pytest.mark.parametrize("K,N", [(768, 2304), (3072, 768)])
+def test_gemm_tc_full_size_properties(dev, K, N):
+    """The batched configuration's prefill GEMMs at full size (M = 8192 rows), checked through properties that do
+    not need a CPU product of the whole matrix: integer operands are exact (every tile, every k-block and the
+    persistent tile loop contribute an integer that float64 reproduces on a row sample), additivity in A, a row
+    sample of a random product against float64, and bit-identical repeats."""
+    from webgpt_b200 import _lib
+    M = 8192
+    rng = np.random.default_rng(K)
+    rows = rng.choice(M, 96, replace=False)
+    Ai = rng.integers(-3, 4, (M, K)).astype(np.float32)
+    Wi = rng.integers(-3, 4, (N, K)).astype(np.float32)
+    zero = np.zeros(N, np.float32)
+    for mode in (_lib.PRECISION_TF32, _lib.PRECISION_TF32X3):
+        got = run_nk(dev, Ai, Wi, zero, mode)
+        assert np.array_equal(got[rows].astype(np.float64), Ai[rows].astype(np.float64) @ Wi.astype(np.float64).T)
+        assert got.sum(dtype=np.float64) == (Ai.sum(0, dtype=np.float64) @ Wi.astype(np.float64).T).sum()
+    A1 = rng.standard_normal((M, K), dtype=np.float32)
+    A2 = rng.standard_normal((M, K), dtype=np.float32)
+    Wt = (rng.standard_normal((N, K), dtype=np.float32) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    y1 = run_nk(dev, A1, Wt, b, _lib.PRECISION_TF32X3)
+    y2 = run_nk(dev, A2, Wt, zero, _lib.PRECISION_TF32X3)
+    y12 = run_nk(dev, A1 + A2, Wt, b, _lib.PRECISION_TF32X3)
+    assert rel_err(y12, y1.astype(np.float64) + y2) < TOL_X3
+    ref = A1[rows].astype(np.float64) @ Wt.astype(np.float64).T + b
+    assert rel_err(y1[rows], ref) < TOL_X3
+    assert np.array_equal(run_nk(dev, A1, Wt, b, _lib.PRECISION_TF32X3), y1)
+
+
 def test_model_in_tf32x3_matches_oracle(oracle):
     """Prefill and batched decode through the tensor cores: logits within 1e-3 (required) / 5e-5 (asserted)."""
     from webgpt_b200 import GPT, _lib

@@ -520,9 +520,17 @@ static int32_t make_tile_map(CUtensorMap *map, const float *base, uint64_t rows,
   return WGPT_OK;
 }
 
+// A LayerNorm that consumes a product's output (the next block's input): when the product runs split-K, its
+// second stage normalises the finished rows as it writes them (splitk_reduce_ln_kernel) and sets `done`.
+struct LnAfter {
+  const float *gamma, *beta;
+  float *out;  // [M, N]
+  bool done;
+};
+
 // C = A[M,K] (row stride lda) . Wt[N,K]^T on the tensor cores; x3 selects 3 x TF32.
 static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t lda, const float *Wt, int M, int K,
-                              int N, const Epilogue &epi) {
+                              int N, const Epilogue &epi, LnAfter *ln = nullptr) {
   REQUIRE(aligned16(A) && aligned16(Wt) && (lda % 4) == 0 && (K % 4) == 0, WGPT_ERR_ALIGN,
           "tensor-core GEMM operands must be 16-byte aligned with row strides that are multiples of 16 bytes");
   CUtensorMap ma, mb;
@@ -559,17 +567,23 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
                kb_per_split, splits, split_out);
   }
   if (split_out != nullptr) {
-    int n4 = M * (N / 4);
-    LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
+    if (ln != nullptr && N / 4 <= 256 * kReduceLnVec && epi.kc == nullptr) {
+      LAUNCH_PDL(dev, splitk_reduce_ln_kernel, M, 256, 0, (const float *)split_out, splits, M, N, epi, ln->gamma,
+                 ln->beta, ln->out);
+      ln->done = true;
+    } else {
+      int n4 = M * (N / 4);
+      LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
+    }
   }
   return WGPT_OK;
 }
 
 // Matrix product for more than 8 rows against a weight stored [N,K]: tensor cores or CUDA cores per dev->precision.
 static int32_t launch_gemm_nk(wgpt_device *dev, const float *A, size_t lda, const float *Wt, int M, int K, int N,
-                              const Epilogue &epi) {
+                              const Epilogue &epi, LnAfter *ln = nullptr) {
   if (dev->precision == WGPT_PRECISION_FP32) return launch_gemm_simt(dev, true, A, lda, Wt, M, K, N, epi);
-  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, Wt, M, K, N, epi);
+  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, Wt, M, K, N, epi, ln);
 }
 
 static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in, const float *gamma, const float *beta,
@@ -1197,17 +1211,27 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   LAUNCH_PDL(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size,
              (const int *)s->d_pos, dev->d_err);
 
+  // s->h already holds the LayerNorm of s->x that the next product wants (left there by the split-K second
+  // stage of the product that wrote s->x)
+  bool h_ready = false;
   auto mm = [&](const float *a, const float *gamma, const float *beta, const float *Wt, int K, int N,
-                const Epilogue &e) -> int32_t {
-    // a: [M,K] contiguous. Small M: weight-streaming GEMV with the LayerNorm fused in; otherwise a separate
-    // LayerNorm pass into s->h and a tiled GEMM.
+                const Epilogue &e, const float *next_gamma = nullptr, const float *next_beta = nullptr) -> int32_t {
+    // a: [M,K] contiguous. Small M: weight-streaming GEMV with the LayerNorm fused in; otherwise a LayerNorm pass
+    // into s->h (separate, or riding on the previous product's second stage) and a tiled GEMM. next_gamma/beta:
+    // the LayerNorm that will consume this product's output rows e.out[M,N].
     if (gemv_nk_fits(dev, M, K)) return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
     const float *src = a;
     if (gamma) {
-      TRY(launch_layernorm(dev, a, (size_t)K, gamma, beta, s->h, (size_t)K, M, K));
+      if (!h_ready) TRY(launch_layernorm(dev, a, (size_t)K, gamma, beta, s->h, (size_t)K, M, K));
+      h_ready = false;
       src = s->h;
     }
-    return launch_gemm_nk(dev, src, (size_t)K, Wt, M, K, N, e);
+    LnAfter ln = {next_gamma, next_beta, s->h, false};
+    // the product must not read s->h itself while its second stage rewrites it
+    bool can_fuse = next_gamma != nullptr && src != s->h;
+    TRY(launch_gemm_nk(dev, src, (size_t)K, Wt, M, K, N, e, can_fuse ? &ln : nullptr));
+    h_ready = ln.done;
+    return WGPT_OK;
   };
 
   for (int l = 0; l < p.n_layer; l++) {
@@ -1236,10 +1260,10 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
         } else {
           dim3 mg((E / 4 + 127) / 128, M);
           LAUNCH_PDL(dev, attn_merge_kernel, mg, 128, 0, ap, s->o, E);
-          TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+          TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e, L.ln2_g, L.ln2_b));
         }
       } else {
-        TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e));
+        TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e, L.ln2_g, L.ln2_b));
       }
     }
     {  // LN2 + MLP up-projection + GELU
@@ -1250,7 +1274,11 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     {  // MLP down-projection + residual
       Epilogue e = plain_epi(s->x, E, L.bpr);
       e.residual = s->x;
-      TRY(mm(s->f, nullptr, nullptr, L.wpr_t, F, E, e));
+      const bool last = l + 1 == p.n_layer;
+      // the next consumer of s->x: the following block's ln_1, or ln_f when every row is a newest row
+      const float *ng = last ? (n_tok == 1 ? m->lnf_g : nullptr) : m->layers[l + 1].ln1_g;
+      const float *nb = last ? (n_tok == 1 ? m->lnf_b : nullptr) : m->layers[l + 1].ln1_b;
+      TRY(mm(s->f, nullptr, nullptr, L.wpr_t, F, E, e, ng, nb));
     }
   }
   // ln_f + tied de-embedding on the newest row of each sequence only (the reference normalises all rows and
@@ -1271,7 +1299,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     if (pick) s->len += n_tok;
     return WGPT_OK;
   }
-  TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
+  if (!h_ready) TRY(launch_layernorm(dev, x_last, ld_last, m->lnf_g, m->lnf_b, s->h, (size_t)E, s->n_seq, E));
   TRY(launch_gemm_nk(dev, s->h, (size_t)E, m->wte, s->n_seq, E, p.vocab_size, e));
   if (pick) TRY(pick_and_advance(s, n_tok));
   return WGPT_OK;

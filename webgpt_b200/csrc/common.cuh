@@ -55,7 +55,7 @@ __device__ __forceinline__ void epi_store(const Epilogue &e, float v, int m, int
   *epi_addr(e, m, n) = epi_apply(e, v, m, n);
 }
 
-__device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, int n) {
+__device__ __forceinline__ float4 epi_apply4(const Epilogue &e, float4 v, int m, int n) {
   if (e.colscale) {
     float4 c = *reinterpret_cast<const float4 *>(e.colscale + n);
     v.x *= c.x; v.y *= c.y; v.z *= c.z; v.w *= c.w;
@@ -69,7 +69,11 @@ __device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, i
     float4 r = __ldcg(reinterpret_cast<const float4 *>(e.residual + (size_t)m * e.ld + n));
     v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
   }
-  *reinterpret_cast<float4 *>(epi_addr(e, m, n)) = v;
+  return v;
+}
+
+__device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, int n) {
+  *reinterpret_cast<float4 *>(epi_addr(e, m, n)) = epi_apply4(e, v, m, n);
 }
 
 // 128-bit read-only load that does not allocate in L1 (weights are streamed once per pass).

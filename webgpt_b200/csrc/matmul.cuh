@@ -501,6 +501,74 @@ __global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit
   epi_store4(epi, s, m, n);
 }
 
+// Second stage of a split-K product whose consumer is a LayerNorm (the residual stream feeding the next block):
+// one CTA per row adds the slices in order, applies the epilogue (bias, residual) into epi.out, and normalises the
+// finished row, still in registers, into ln_out[M, N] (mean and variance over N as in layernorm_kernel). Saves the
+// separate LayerNorm pass and its read of the row. N <= 4096 (four float4 per thread).
+constexpr int kReduceLnVec = 4;
+__global__ void __launch_bounds__(256)
+splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N, Epilogue epi,
+                        const float *__restrict__ gamma, const float *__restrict__ beta,
+                        float *__restrict__ ln_out) {
+  __shared__ float red[2][8];
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int N4 = N >> 2;
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the previous kernel
+  float4 v[kReduceLnVec];
+  float s = 0.f;
+#pragma unroll
+  for (int r = 0; r < kReduceLnVec; r++) {
+    const int i = tid + 256 * r;
+    v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < N4) {
+      const int n = i * 4;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int k = 0; k < ksplit; k++) {
+        float4 t = __ldcg(reinterpret_cast<const float4 *>(part + ((size_t)k * M + m) * N + n));
+        a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+      }
+      a = epi_apply4(epi, a, m, n);
+      *reinterpret_cast<float4 *>(epi_addr(epi, m, n)) = a;
+      v[r] = a;
+      s += (a.x + a.y) + (a.z + a.w);
+    }
+  }
+  s = warp_sum(s);
+  if (lane == 0) red[0][warp] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; w++) tot += red[0][w];
+  const float mean = tot / (float)N;
+  float q = 0.f;
+#pragma unroll
+  for (int r = 0; r < kReduceLnVec; r++) {
+    if (tid + 256 * r < N4) {
+      float a = v[r].x - mean, b = v[r].y - mean, c = v[r].z - mean, d = v[r].w - mean;
+      q += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  q = warp_sum(q);
+  if (lane == 0) red[1][warp] = q;
+  __syncthreads();
+  float qt = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; w++) qt += red[1][w];
+  const float sd = sqrtf(qt / (float)N + 1e-5f);
+#pragma unroll
+  for (int r = 0; r < kReduceLnVec; r++) {
+    const int i = tid + 256 * r;
+    if (i < N4) {
+      float4 g = *reinterpret_cast<const float4 *>(gamma + 4 * i), b = *reinterpret_cast<const float4 *>(beta + 4 * i);
+      *reinterpret_cast<float4 *>(ln_out + (size_t)m * N + 4 * i) =
+          make_float4(g.x * ((v[r].x - mean) / sd) + b.x, g.y * ((v[r].y - mean) / sd) + b.y,
+                      g.z * ((v[r].z - mean) / sd) + b.z, g.w * ((v[r].w - mean) / sd) + b.w);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // C[M,N] = A[M,K] . B (+ epilogue). A rows at stride lda. B is [K,N] (B_NK = false, the reference layout)
 // or [N,K] (B_NK = true). K % 4 == 0, N % 4 == 0. 256 threads, 64x64 tile, 16-deep K step.
