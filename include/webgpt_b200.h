@@ -99,7 +99,11 @@ int32_t wgpt_graph_end(wgpt_device *dev, wgpt_graph **out);
 int32_t wgpt_graph_launch(wgpt_device *dev, wgpt_graph *graph);
 int32_t wgpt_graph_destroy(wgpt_device *dev, wgpt_graph *graph);
 
-/* ---- per-operator entry points: one per instruction class of instructions.js ---- */
+/* ---- per-operator entry points: one per instruction class of instructions.js ----
+ * Parameter buffers (weights, bias, gamma, beta, scales) are treated as constants of the model: a kernel may read
+ * them before the operation enqueued just ahead of it has finished. Fill them with wgpt_buffer_write /
+ * wgpt_buffer_copy (copies are fully ordered), or call wgpt_device_synchronize between an operator that writes such
+ * a buffer and the operator that uses it as a parameter. Inputs and outputs carry no such restriction. */
 
 /* FastMatMulBlock.newInstance(rows, cols, shared, input, weights, bias) (instructions.js:157-177),
  * kernel fastMatMul (:179-319): out[rows,cols] = in[rows,shared] . W[shared,cols] + bias[cols].

@@ -530,7 +530,7 @@ struct LnAfter {
 
 // C = A[M,K] (row stride lda) . Wt[N,K]^T on the tensor cores; x3 selects 3 x TF32.
 static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t lda, const float *Wt, int M, int K,
-                              int N, const Epilogue &epi, LnAfter *ln = nullptr) {
+                              int N, const Epilogue &epi, LnAfter *ln = nullptr, bool b_static = true) {
   REQUIRE(aligned16(A) && aligned16(Wt) && (lda % 4) == 0 && (K % 4) == 0, WGPT_ERR_ALIGN,
           "tensor-core GEMM operands must be 16-byte aligned with row strides that are multiples of 16 bytes");
   CUtensorMap ma, mb;
@@ -546,34 +546,43 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
     if (want > total_kb) want = total_kb;
     kb_per_split = (total_kb + want - 1) / want;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
-    if (splits > 1 && (size_t)splits * M * N * 4 <= dev->tc_scratch_bytes && (N % 4) == 0) {
+    const size_t n_pad = (size_t)((N + TC_BM - 1) / TC_BM) * TC_BM;  // the exchanged form stores whole feature tiles
+    if (splits > 1 && (size_t)splits * M * n_pad * 4 <= dev->tc_scratch_bytes && (N % 4) == 0) {
       split_out = dev->tc_scratch;
     } else {
       splits = 1;
       kb_per_split = total_kb;
     }
   }
+  // Skinny split-K products run with the operands exchanged: the kernel sees C^T[N,M] = Wt[N,K] . A[M,K]^T, so the
+  // accumulator's 128 lanes are output features (all live) and its columns the few activation rows; the partial
+  // tiles are written feature-tile-major, which the second stage reads with tile width 128.
+  const bool exchanged = split_out != nullptr && M <= 64;
+  const int tw = exchanged ? TC_BM : N;
   const int n_work = tiles * splits;
   dim3 grid(n_work < dev->sm_count ? n_work : dev->sm_count);
+  const CUtensorMap &m_first = exchanged ? mb : ma, &m_second = exchanged ? ma : mb;
+  const int km = exchanged ? N : M, kn = exchanged ? M : N;
+  const int static_op = b_static ? (exchanged ? 2 : 1) : 0;
   if (x3) {
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
-               kb_per_split, splits, split_out);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, m_first, m_second, km, K, kn, epi,
+               dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0);
   } else {
     auto kern = gemm_tc_kernel<false>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, M, K, N, epi, dev->d_err,
-               kb_per_split, splits, split_out);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, m_first, m_second, km, K, kn, epi,
+               dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0);
   }
   if (split_out != nullptr) {
     if (ln != nullptr && N / 4 <= 256 * kReduceLnVec && epi.kc == nullptr) {
       LAUNCH_PDL(dev, splitk_reduce_ln_kernel, M, 256, 0, (const float *)split_out, splits, M, N, epi, ln->gamma,
-                 ln->beta, ln->out);
+                 ln->beta, ln->out, tw);
       ln->done = true;
     } else {
       int n4 = M * (N / 4);
-      LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi);
+      LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, (const float *)split_out, splits, M, N, epi, tw);
     }
   }
   return WGPT_OK;
@@ -628,7 +637,7 @@ static int32_t gemv_kn_with_scratch(wgpt_device *dev, int M, const float *x, con
     default: return fail(WGPT_ERR_SHAPE, "gemv rows %d out of range", M);
   }
   int n4 = M * (N / 4);
-  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, epi);
+  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, epi, N);
   return WGPT_OK;
 }
 
@@ -874,7 +883,8 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
       float *wt = static_cast<float *>(dev->scratch);
       dim3 xgrid((N / 4 + 31) / 32, (K + 31) / 32);
       LAUNCH(dev, int8_expand_nk_kernel, xgrid, 256, 0, Bq, K, N, wt);
-      return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e);
+      // the expanded weight was written by the kernel just before: no reads of it ahead of the dependency wait
+      return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false);
     }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     LAUNCH(dev, int8_gemm_simt_kernel, grid, 256, 0, A, Bq, M, K, N, e);
@@ -898,7 +908,7 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
 #undef CASE_W
 #undef CASE_N
   int n4 = M * (N / 4);
-  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, e);
+  LAUNCH_PDL(dev, gemv_kn_reduce_kernel, (n4 + 255) / 256, 256, 0, part, ksplit, M, N, e, N);
   return WGPT_OK;
 }
 

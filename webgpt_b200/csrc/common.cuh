@@ -97,13 +97,13 @@ __device__ __forceinline__ uint4 ldg_stream4u(const uint4 *p) {
 #ifdef WGPT_TRACE
 __device__ unsigned long long g_trace_buf[1 << 17];
 __device__ unsigned int g_trace_n;
-// One atomic per kernel (at entry, ahead of the dependency wait) reserves 8 record slots; later phases only read
+// One atomic per kernel (at entry, ahead of the dependency wait) reserves 32 record slots; later phases only read
 // the timer and store, so they do not stall the traced thread.
 __device__ __forceinline__ unsigned int trace_begin(int kid) {
   unsigned int base = 0xffffffffu;
   if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
-    base = atomicAdd(&g_trace_n, 8u);
-    if (base + 8 > (1u << 16)) base = 0xffffffffu;
+    base = atomicAdd(&g_trace_n, 32u);
+    if (base + 32 > (1u << 16)) base = 0xffffffffu;
   }
   return base;
 }

@@ -84,6 +84,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
   for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
 }
 
+// 128-bit accesses in the shared state space by 32-bit address (a pointer derived from the dynamic shared-memory
+// base by integer arithmetic would otherwise be accessed generically).
+__device__ __forceinline__ float4 lds128(uint32_t saddr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t saddr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(saddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes with the 128-byte swizzle
 // (what TMA writes for a {32 floats, rows} box): start address, stride between 8-row groups = 1024 bytes,
 // descriptor version 1, swizzle mode 2 (128 B). The tile base must be 1024-byte aligned; advancing by k*32
@@ -107,6 +118,7 @@ struct TcPlan {
   static constexpr int kStages = X3 ? 3 : 6;
   static constexpr int kStageBytes = (X3 ? 4 : 2) * TC_TILE_BYTES;
   static constexpr int kThreads = X3 ? 320 : 192;
+  // dynamic part: alignment slack + stages + barriers and flags (512 bytes)
   static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + 512;
 };
 
@@ -133,7 +145,8 @@ __device__ __forceinline__ TcWork tc_work(int w, int m_tiles, int n_tiles, int k
 template <bool X3>
 __global__ void __launch_bounds__(TcPlan<X3>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int K,
-               int N, Epilogue epi, int *err, int kb_per_split, int splits, float *split_out) {
+               int N, Epilogue epi, int *err, int kb_per_split, int splits, float *split_out, int static_op,
+               int transposed) {
   using Plan = TcPlan<X3>;
   constexpr int S = Plan::kStages;
   extern __shared__ uint8_t tc_smem_raw[];
@@ -143,11 +156,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t *acc_full = bars + 3 * S, *acc_empty = bars + 3 * S + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // transposition pads of the epilogue warps: a static array, so that the compiler addresses it as shared memory
+  __shared__ float epi_pad[4 * 32 * 33];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + TC_BN - 1) / TC_BN;
   const int n_work = m_tiles * n_tiles * splits;
+#ifdef WGPT_TRACE
+  __shared__ unsigned int tc_trace_base;  // the roles below are different threads: they share thread 0's record
+  {
+    TRACE_BEGIN(5);
+    trace(5, 0);
+    if (threadIdx.x == 0) tc_trace_base = trace_base_;
+  }
+#define TC_TRACE(phase) do { if (lane == 0) trace_at(tc_trace_base, 5, phase); } while (0)
+#else
+#define TC_TRACE(phase) ((void)0)
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; i++) {
@@ -168,8 +194,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp == 0) TC_TRACE(1);
   pdl_launch_dependents();
+  // static_op names the operand that does not depend on the previous kernel (model weights, written long before):
+  // 1 = B, 2 = A, 0 = neither. The producer requests that operand's tiles of its first work item's first k-blocks
+  // (one per pipeline stage) before the dependency wait, so that their HBM latency overlaps the tail of the
+  // previous kernel. The other operand's tiles follow after the wait.
+  int pre = 0;
+  if (static_op != 0 && warp == 0 && lane == 0 && (int)blockIdx.x < n_work) {
+    const TcWork t = tc_work(blockIdx.x, m_tiles, n_tiles, kb_per_split, total_kb);
+    pre = t.num_kb < S ? t.num_kb : S;
+    for (int kb = 0; kb < pre; kb++) {
+      uint8_t *st = tiles + (size_t)kb * Plan::kStageBytes;
+      mbar_expect_tx(&full[kb], 2 * TC_TILE_BYTES);
+      if (static_op == 1)
+        tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[kb]);
+      else
+        tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[kb]);
+    }
+  }
   pdl_wait();  // A (activations) comes from the previous kernel
+  if (warp == 0) TC_TRACE(2);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -179,13 +224,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
         for (int kb = 0; kb < t.num_kb; kb++, kc++) {
           const int s = kc % S, it = kc / S;
-          if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
           uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
+          if (kc < pre) {  // first use of the stage; the static operand's tile is already on the way
+            if (static_op == 1)
+              tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[s]);
+            else
+              tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
+            continue;
+          }
+          if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
           mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
           tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[s]);
           tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
         }
+        if (w == blockIdx.x) TC_TRACE(3);
       }
+      TC_TRACE(14);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -202,6 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint64_t *go = X3 ? &ready[s] : &full[s];
           if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS)) { *abort_flag = 1; break; }
           tc_fence_after();
+          if (kc == 0) TC_TRACE(4);
           const uint32_t a_hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes);
           const uint32_t b_hi = a_hi + TC_TILE_BYTES;
 #pragma unroll
@@ -218,7 +273,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
         umma_commit(&acc_full[buf]);  // this tile's accumulator is complete (also reached after an abort)
+        if (i == 0) TC_TRACE(5);
       }
+      TC_TRACE(13);
     }
   } else if (warp < 6) {
     // ---------------- epilogue: accumulator lanes 32*(warp%4).. ----------------
@@ -230,6 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool ok = mbar_wait(&acc_full[buf], use & 1, TC_POLLS << 4) && !*abort_flag;
       if (!ok) { *abort_flag = 1; break; }
       tc_fence_after();
+      if (i == 0 && warp == 2) TC_TRACE(6);
       Epilogue e = epi;
       if (split_out != nullptr) {  // raw partial tile of K slice z; a second kernel sums the slices in order
         e.colscale = nullptr; e.bias = nullptr; e.residual = nullptr; e.kc = nullptr; e.vc = nullptr;
@@ -238,33 +296,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         e.ld = N;
       }
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TC_BN);
-      const int m = t.m0 + quad * 32 + lane;
+      if (transposed) {
+        // Skinny products run with the operands exchanged (kernel rows = output features, kernel columns = the
+        // few activation rows), always split-K: all four warps hold live lanes, only ceil(N/32) column chunks are
+        // live, and for a fixed activation row the 32 lanes are 32 consecutive features, so the raw partials go
+        // out as 128-byte stores without a transposition. Layout: [z][feature tile][activation row][128].
+        float *tile_out = split_out + ((size_t)t.z * m_tiles + t.m0 / TC_BM) * (size_t)N * TC_BM + quad * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < TC_BN / 32; c++) {
+          const int nb = c * 32;
+          float v[32];
+          if (nb < N) tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)nb, v);
+          if (c == TC_BN / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(&acc_empty[buf]);
+          }
+          if (nb >= N) continue;
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (nb + j < N) tile_out[(size_t)(nb + j) * TC_BM] = v[j];
+        }
+        continue;
+      }
+      // A lane of the accumulator is an output row, so the values a thread reads back lie along one row while
+      // the 32 lanes of the warp are 32 different rows. Storing from there would scatter every warp-wide store
+      // over 32 rows; each 32 x 32 block is transposed through a padded shared-memory tile instead, after which a
+      // warp-wide float4 store covers four rows x 128 contiguous bytes (and the residual reads coalesce too).
+      float *pad = epi_pad + (warp - 2) * (32 * 33);
+      const int row0 = t.m0 + quad * 32;
+      const bool rows_live = row0 < M;  // a tile hanging over the last row: nothing to store from these lanes
       const bool vec_ok = ((N | e.ld) & 3) == 0;
+      const int sub_r = lane >> 3, col4 = (lane & 7) * 4;
 #pragma unroll 1
       for (int c = 0; c < TC_BN / 32; c++) {
         float v[32];
-        tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+        if (rows_live) tmem_ld_32x32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
         if (c == TC_BN / 32 - 1) {  // everything is in registers: hand the accumulator back before storing
           tc_fence_before();
           mbar_arrive(&acc_empty[buf]);
         }
-        if (m < M) {
-          const int nb = t.n0 + c * 32;
+        const int nb = t.n0 + c * 32;
+        if (!rows_live || nb >= N) continue;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int n = nb + j;
-            if (n >= N) break;
+        for (int j = 0; j < 32; j++) pad[lane * 33 + j] = v[j];
+        __syncwarp();
+#pragma unroll 1
+        for (int it = 0; it < 8; it++) {
+          const int r = it * 4 + sub_r;
+          const int m = row0 + r, n = nb + col4;
+          const float *src = pad + r * 33 + col4;
+          const float4 x = make_float4(src[0], src[1], src[2], src[3]);
+          if (m < M && n < N) {
             if (vec_ok) {
-              epi_store4(e, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]), m, n);
+              epi_store4(e, x, m, n);
             } else {
-#pragma unroll
-              for (int q = 0; q < 4; q++)
-                if (n + q < N) epi_store(e, v[j + q], m, n + q);
+              epi_store(e, x.x, m, n);
+              if (n + 1 < N) epi_store(e, x.y, m, n + 1);
+              if (n + 2 < N) epi_store(e, x.z, m, n + 2);
+              if (n + 3 < N) epi_store(e, x.w, m, n + 3);
             }
           }
         }
+        __syncwarp();
       }
     }
+    if (warp == 2) TC_TRACE(7);
+    if (warp == 4) TC_TRACE(10);
+    if (warp == 5) TC_TRACE(11);
     tc_fence_before();
   } else if (X3) {
     // ---------------- hi/lo split (warps 6-9) ----------------
@@ -276,30 +374,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int s = kc % S, it = kc / S;
         if (*abort_flag || !mbar_wait(&full[s], it & 1, TC_POLLS)) { *abort_flag = 1; break; }
         // A and B tiles are adjacent (32 KiB); the lo copies sit 32 KiB further. Element order does not matter.
-        float4 *hi = reinterpret_cast<float4 *>(tiles + (size_t)s * Plan::kStageBytes);
-        float4 *lo = hi + (2 * TC_TILE_BYTES) / 16;
-#pragma unroll 4
-        for (int q = tix; q < (2 * TC_TILE_BYTES) / 16; q += 128) {
+        const uint32_t hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes) + (uint32_t)tix * 16u;
+        const uint32_t lo = hi + 2 * TC_TILE_BYTES;
+#pragma unroll 8
+        for (int q = 0; q < (2 * TC_TILE_BYTES) / (16 * 128); q++) {
           // kind::tf32 reads the top 19 bits of each FP32 operand and ignores the rest (checked on B200: clearing
           // the low 13 bits first gives bit-identical products), so the staged tile itself serves as `hi`.
-          float4 x = hi[q], l;
+          float4 x = lds128(hi + (uint32_t)q * 2048u), l;
           l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
           l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
           l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
           l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-          lo[q] = l;
+          sts128(lo + (uint32_t)q * 2048u, l);
         }
         fence_async_smem();  // make these generic-proxy writes visible to the tensor core's reads
         mbar_arrive(&ready[s]);
       }
     }
+    if (warp == 6) TC_TRACE(12);
   }
 
   __syncthreads();
+  if (warp == 0) TC_TRACE(8);
   if (threadIdx.x == 0 && *abort_flag) atomicExch(err, 3);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * TC_BN);
+    TC_TRACE(9);
   }
 }
 

@@ -485,36 +485,47 @@ gemv_kn_partial_kernel(const float *__restrict__ x, const float *__restrict__ W,
   }
 }
 
-__global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit, int M, int N, Epilogue epi) {
+// part: [ksplit][N / tw column tiles][M][tw] (tw = N: plain [ksplit][M][N]); tw % 4 == 0.
+__global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit, int M, int N, Epilogue epi, int tw) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;  // float4 index over [M, N/4]
   int N4 = N >> 2;
+  TRACE_BEGIN(6);
+  trace(6, 0);
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the previous kernel
+  trace(6, 1);
   if (i >= M * N4) return;
   int m = i / N4, n = (i - m * N4) * 4;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int n_tiles = (N + tw - 1) / tw, nt = n / tw;
+  const float *p0 = part + ((size_t)nt * M + m) * tw + (n - nt * tw);
+  const size_t zstride = (size_t)n_tiles * M * tw;
 #pragma unroll 4
   for (int k = 0; k < ksplit; k++) {
-    float4 v = __ldcg(reinterpret_cast<const float4 *>(part + ((size_t)k * M + m) * N + n));
+    float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
   epi_store4(epi, s, m, n);
+  trace(6, 2);
 }
 
 // Second stage of a split-K product whose consumer is a LayerNorm (the residual stream feeding the next block):
-// one CTA per row adds the slices in order, applies the epilogue (bias, residual) into epi.out, and normalises the
+// one CTA per row adds the slices in order (layout as in gemv_kn_reduce_kernel), applies the epilogue (bias, residual) into epi.out, and normalises the
 // finished row, still in registers, into ln_out[M, N] (mean and variance over N as in layernorm_kernel). Saves the
 // separate LayerNorm pass and its read of the row. N <= 4096 (four float4 per thread).
 constexpr int kReduceLnVec = 4;
 __global__ void __launch_bounds__(256)
 splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N, Epilogue epi,
                         const float *__restrict__ gamma, const float *__restrict__ beta,
-                        float *__restrict__ ln_out) {
+                        float *__restrict__ ln_out, int tw) {
   __shared__ float red[2][8];
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N4 = N >> 2;
+  TRACE_BEGIN(7);
+  trace(7, 0);
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the previous kernel
+  trace(7, 1);
   float4 v[kReduceLnVec];
   float s = 0.f;
 #pragma unroll
@@ -524,9 +535,12 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
     if (i < N4) {
       const int n = i * 4;
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int n_tiles = (N + tw - 1) / tw, nt = n / tw;
+      const float *p0 = part + ((size_t)nt * M + m) * tw + (n - nt * tw);
+      const size_t zstride = (size_t)n_tiles * M * tw;
 #pragma unroll 4
       for (int k = 0; k < ksplit; k++) {
-        float4 t = __ldcg(reinterpret_cast<const float4 *>(part + ((size_t)k * M + m) * N + n));
+        float4 t = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
         a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
       }
       a = epi_apply4(epi, a, m, n);
@@ -567,6 +581,7 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
                       g.z * ((v[r].z - mean) / sd) + b.z, g.w * ((v[r].w - mean) / sd) + b.w);
     }
   }
+  trace(7, 2);
 }
 
 // ------------------------------------------------------------------------------------------------
