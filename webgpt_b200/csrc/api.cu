@@ -557,7 +557,9 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   // Skinny split-K products run with the operands exchanged: the kernel sees C^T[N,M] = Wt[N,K] . A[M,K]^T, so the
   // accumulator's 128 lanes are output features (all live) and its columns the few activation rows; the partial
   // tiles are written feature-tile-major, which the second stage reads with tile width 128.
-  const bool exchanged = split_out != nullptr && M <= 64;
+  // Without split-K (a very wide product such as the de-embedding of up to 64 sequences) the exchanged form
+  // finishes the values itself; it carries no activation or cache scatter.
+  const bool exchanged = M <= 64 && (split_out != nullptr || (epi.act == 0 && epi.kc == nullptr));
   const int tw = exchanged ? TC_BM : N;
   const int n_work = tiles * splits;
   dim3 grid(n_work < dev->sm_count ? n_work : dev->sm_count);

@@ -120,9 +120,21 @@ __global__ void argmax_kernel(const float *__restrict__ logits, int V, uint32_t 
   const float *x = logits + (size_t)seq * V;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  // eight loads in flight per thread (few CTAs run: the row scan is bound by latency, not bandwidth); a thread's
+  // indices ascend, so a strict > keeps its lowest index among equal values
+  int i = threadIdx.x;
+  const int stride = blockDim.x;
+  for (; i + 7 * stride < V; i += 8 * stride) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) v[u] = __ldcg(x + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 8; u++)
+      if (v[u] > best) { best = v[u]; bi = i + u * stride; }
+  }
+  for (; i < V; i += stride) {
     float v = __ldcg(x + i);
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    if (v > best) { best = v; bi = i; }
   }
   __shared__ float sv[32];
   __shared__ int si[32];

@@ -298,10 +298,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TC_BN);
       if (transposed) {
         // Skinny products run with the operands exchanged (kernel rows = output features, kernel columns = the
-        // few activation rows), always split-K: all four warps hold live lanes, only ceil(N/32) column chunks are
-        // live, and for a fixed activation row the 32 lanes are 32 consecutive features, so the raw partials go
-        // out as 128-byte stores without a transposition. Layout: [z][feature tile][activation row][128].
-        float *tile_out = split_out + ((size_t)t.z * m_tiles + t.m0 / TC_BM) * (size_t)N * TC_BM + quad * 32 + lane;
+        // few activation rows): all four warps hold live lanes, only ceil(N/32) column chunks are live, and for a
+        // fixed activation row the 32 lanes are 32 consecutive features, so every store is 128 contiguous bytes
+        // without a transposition. Split-K: raw partials, layout [z][feature tile][activation row][128].
+        // Otherwise the finished value with scale, bias and residual (no activation or cache scatter in this form).
+        const int feat = t.m0 + quad * 32 + lane;
+        float *tile_out = split_out != nullptr
+                              ? split_out + ((size_t)t.z * m_tiles + t.m0 / TC_BM) * (size_t)N * TC_BM + quad * 32 + lane
+                              : nullptr;
+        const bool feat_ok = feat < M;
+        const float cs = (tile_out == nullptr && epi.colscale && feat_ok) ? epi.colscale[feat] : 1.f;
+        const float bs = (tile_out == nullptr && epi.bias && feat_ok) ? epi.bias[feat] : 0.f;
 #pragma unroll 1
         for (int c = 0; c < TC_BN / 32; c++) {
           const int nb = c * 32;
@@ -312,9 +319,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_arrive(&acc_empty[buf]);
           }
           if (nb >= N) continue;
+          if (tile_out != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            if (nb + j < N) tile_out[(size_t)(nb + j) * TC_BM] = v[j];
+            for (int j = 0; j < 32; j++)
+              if (nb + j < N) tile_out[(size_t)(nb + j) * TC_BM] = v[j];
+          } else if (feat_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              if (nb + j < N) {
+                const size_t at = (size_t)(nb + j) * epi.ld + feat;
+                float x = v[j] * cs + bs;
+                if (epi.residual) x += __ldcg(epi.residual + at);
+                epi.out[at] = x;
+              }
+            }
+          }
         }
         continue;
       }

@@ -538,8 +538,16 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
       const int n_tiles = (N + tw - 1) / tw, nt = n / tw;
       const float *p0 = part + ((size_t)nt * M + m) * tw + (n - nt * tw);
       const size_t zstride = (size_t)n_tiles * M * tw;
-#pragma unroll 4
-      for (int k = 0; k < ksplit; k++) {
+      // eight slices in flight per thread: the row is short and few CTAs run, so the loop is bound by latency
+      int k = 0;
+      for (; k + 8 <= ksplit; k += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) t[u] = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(k + u) * zstride));
+#pragma unroll
+        for (int u = 0; u < 8; u++) { a.x += t[u].x; a.y += t[u].y; a.z += t[u].z; a.w += t[u].w; }
+      }
+      for (; k < ksplit; k++) {
         float4 t = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
         a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
       }

@@ -55,9 +55,22 @@ sample_topk_kernel(const float *__restrict__ logits, int V, int top_k, double te
   const float *x = logits + (size_t)seq * V;
 
   unsigned long long best = 0ull;  // below every real key (their low word is never zero for idx < 2^32 - 1)
-  for (int i = tid; i < V; i += kSampleThreads) {
-    unsigned long long c = sample_key(__ldcg(x + i), i);
-    best = c > best ? c : best;
+  {
+    int i = tid;  // eight loads in flight per thread: one CTA scans the row, so latency is what bounds it
+    for (; i + 7 * kSampleThreads < V; i += 8 * kSampleThreads) {
+      float f[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) f[u] = __ldcg(x + i + u * kSampleThreads);
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        unsigned long long c = sample_key(f[u], i + u * kSampleThreads);
+        best = c > best ? c : best;
+      }
+    }
+    for (; i < V; i += kSampleThreads) {
+      unsigned long long c = sample_key(__ldcg(x + i), i);
+      best = c > best ? c : best;
+    }
   }
   srt[tid] = best;
   if (tid == 0) s_cnt = 0;
