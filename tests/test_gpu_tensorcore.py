@@ -115,3 +115,32 @@ def test_model_in_tf32x3_matches_oracle(oracle):
             assert np.array_equal(batch[i], m.generate_greedy(prompts[i], 10)[9:])
     finally:
         gpt.destroy()
+
+
+def test_batched_decode_gpt2_width(oracle):
+    """GPT-2 width (d = 768, 12 heads of 64) cut to two layers, 16 and 64 sequences decoded together: the layer
+    products run split-K with exchanged operands, the attention adds the QKV slices itself, the residual products'
+    second stage applies the next LayerNorm, and the de-embedding runs without split. Tokens must equal the
+    oracle's for every checked sequence, logits within 5e-5."""
+    from webgpt_b200 import GPT
+    params = dict(n_layer=2, n_head=12, n_embd=768, n_ctx=48, vocab_size=1000)
+    w = synth.make_weights(params, seed=31, std=0.05, ln_random=True)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    gpt = GPT(None, params=params, weights=w)
+    gpt.initialize()
+    try:
+        for n_seq in (16, 64):
+            prompts = np.stack([synth.make_tokens(params["vocab_size"], 7, seed=50, stream=i) for i in range(n_seq)])
+            batch = gpt.session(n_seq).generate_greedy(prompts, 12)
+            for i in (0, n_seq // 2, n_seq - 1):
+                assert np.array_equal(batch[i], m.kv_generate_greedy(prompts[i], 12)), (n_seq, i)
+            # logits of one more decode step of every sequence against the oracle's recompute
+            s = gpt.session(n_seq)
+            s.reset()
+            s.forward(prompts, want_logits=False)
+            lg = s.forward(batch[:, :1])
+            for i in (1, n_seq - 2):
+                ref = m.run(np.concatenate([prompts[i], batch[i, :1]]))
+                assert rel_err(lg[i], ref) < 5e-5
+    finally:
+        gpt.destroy()

@@ -528,9 +528,18 @@ struct LnAfter {
   bool done;
 };
 
+// A consumer that adds the split-K slices itself (the decode attention for the QKV product): when the product
+// runs split-K in the exchanged form its second stage is not launched and the slices are handed over.
+struct SplitHandoff {
+  const float *part = nullptr;
+  int splits = 0;
+  bool taken = false;
+};
+
 // C = A[M,K] (row stride lda) . Wt[N,K]^T on the tensor cores; x3 selects 3 x TF32.
 static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t lda, const float *Wt, int M, int K,
-                              int N, const Epilogue &epi, LnAfter *ln = nullptr, bool b_static = true) {
+                              int N, const Epilogue &epi, LnAfter *ln = nullptr, bool b_static = true,
+                              const float *Wt_lo = nullptr, SplitHandoff *handoff = nullptr) {
   REQUIRE(aligned16(A) && aligned16(Wt) && (lda % 4) == 0 && (K % 4) == 0, WGPT_ERR_ALIGN,
           "tensor-core GEMM operands must be 16-byte aligned with row strides that are multiples of 16 bytes");
   CUtensorMap ma, mb;
@@ -543,7 +552,8 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   float *split_out = nullptr;
   if (tiles * 2 <= dev->sm_count && total_kb > 1 && dev->tc_scratch != nullptr) {
     int want = (dev->sm_count + tiles - 1) / tiles;
-    if (want > total_kb) want = total_kb;
+    if (want > total_kb / 2) want = total_kb / 2;  // at least two k-blocks per slice: fewer slices to add up
+    if (want < 1) want = 1;
     kb_per_split = (total_kb + want - 1) / want;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
     const size_t n_pad = (size_t)((N + TC_BM - 1) / TC_BM) * TC_BM;  // the exchanged form stores whole feature tiles
@@ -566,16 +576,27 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   const CUtensorMap &m_first = exchanged ? mb : ma, &m_second = exchanged ? ma : mb;
   const int km = exchanged ? N : M, kn = exchanged ? M : N;
   const int static_op = b_static ? (exchanged ? 2 : 1) : 0;
+  // Compute-bound 3xTF32 products read the weight's precomputed low part (x - tf32(x), same layout) by TMA
+  // instead of deriving it in shared memory; skinny products are HBM-bound on the weights and keep deriving it.
+  const bool lo_tma = x3 && Wt_lo != nullptr && !exchanged && b_static;
+  CUtensorMap mlo = mb;
+  if (lo_tma) TRY(make_tile_map(&mlo, Wt_lo, (uint64_t)N, (uint64_t)K, (uint64_t)K));
   if (x3) {
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, m_first, m_second, km, K, kn, epi,
-               dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, m_first, m_second, mlo, km, K, kn,
+               epi, dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0, lo_tma ? 1 : 0);
   } else {
     auto kern = gemm_tc_kernel<false>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
-    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, m_first, m_second, km, K, kn, epi,
-               dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0);
+    LAUNCH_PDL(dev, kern, grid, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, m_first, m_second, mlo, km, K, kn,
+               epi, dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0, 0);
+  }
+  if (split_out != nullptr && handoff != nullptr && exchanged) {
+    handoff->part = split_out;
+    handoff->splits = splits;
+    handoff->taken = true;
+    return WGPT_OK;
   }
   if (split_out != nullptr) {
     if (ln != nullptr && N / 4 <= 256 * kReduceLnVec && epi.kc == nullptr) {
@@ -592,9 +613,11 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
 
 // Matrix product for more than 8 rows against a weight stored [N,K]: tensor cores or CUDA cores per dev->precision.
 static int32_t launch_gemm_nk(wgpt_device *dev, const float *A, size_t lda, const float *Wt, int M, int K, int N,
-                              const Epilogue &epi, LnAfter *ln = nullptr) {
+                              const Epilogue &epi, LnAfter *ln = nullptr, const float *Wt_lo = nullptr,
+                              SplitHandoff *handoff = nullptr) {
   if (dev->precision == WGPT_PRECISION_FP32) return launch_gemm_simt(dev, true, A, lda, Wt, M, K, N, epi);
-  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, Wt, M, K, N, epi, ln);
+  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, Wt, M, K, N, epi, ln, true, Wt_lo,
+                        handoff);
 }
 
 static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in, const float *gamma, const float *beta,
@@ -679,12 +702,24 @@ static int32_t launch_attn_prefill(wgpt_device *dev, int hs, const float *q, int
 
 static int32_t launch_attn_decode(wgpt_device *dev, int hs, const float *q, int ldq, const float *kc, const float *vc,
                                   int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_seq, int H, int n_split,
-                                  const int *pos, float scale, float *part) {
+                                  const int *pos, float scale, float *part, const QkvPartials *qp = nullptr) {
   dim3 grid(H, n_seq, n_split);
+  if (qp != nullptr) {  // the attention CTAs are the QKV product's second stage (one position slice, 3*hs <= 256)
+    switch (hs) {
+#define CASE_Q(HSV)                                                                                                  \
+  case HSV:                                                                                                          \
+    LAUNCH_PDL(dev, (attn_decode_kernel<HSV, true>), grid, 256, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, \
+               scale, part, *qp);                                                                                    \
+    return WGPT_OK;
+      CASE_Q(4) CASE_Q(8) CASE_Q(16) CASE_Q(32) CASE_Q(64)
+#undef CASE_Q
+    }
+    return fail(WGPT_ERR_UNSUPPORTED, "head_size %d with fused QKV second stage", hs);
+  }
 #define CASE(HSV)                                                                                                   \
   case HSV:                                                                                                         \
     LAUNCH_PDL(dev, attn_decode_kernel<HSV>, grid, 256, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, pos, scale, \
-               part);                                                                                               \
+               part, QkvPartials());                                                                                \
     return WGPT_OK;
   switch (hs) {
     CASE(4) CASE(8) CASE(16) CASE(32) CASE(64) CASE(128)
@@ -917,6 +952,8 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
 // ------------------------------------------------------------------------------------------ model
 struct LayerWeights {
   float *ln1_g, *ln1_b, *wqkv_t, *bqkv, *wo_t, *bo, *ln2_g, *ln2_b, *wfc_t, *bfc, *wpr_t, *bpr;
+  // low parts of the four matrices for 3xTF32 (w - tf32(w), same [N,K] layout), filled by wgpt_model_finalize
+  float *wqkv_lo = nullptr, *wo_lo = nullptr, *wfc_lo = nullptr, *wpr_lo = nullptr;
 };
 
 struct wgpt_model {
@@ -1064,6 +1101,19 @@ WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
     lp[i] = LayerPtrs{L.ln1_g, L.ln1_b, L.wqkv_t, L.bqkv, L.wo_t, L.bo, L.ln2_g, L.ln2_b, L.wfc_t, L.bfc, L.wpr_t, L.bpr};
   }
   TRY(use(m->dev));
+  {
+    const size_t E = m->p.n_embd, F = 4 * E;
+    for (auto &L : m->layers) {
+      struct { const float *src; float **dst; size_t n; } jobs[4] = {
+          {L.wqkv_t, &L.wqkv_lo, 3 * E * E}, {L.wo_t, &L.wo_lo, E * E}, {L.wfc_t, &L.wfc_lo, F * E}, {L.wpr_t, &L.wpr_lo, E * F}};
+      for (auto &j : jobs) {
+        if (*j.dst == nullptr) TRY(model_alloc(m, j.dst, j.n));
+        size_t n4 = j.n / 4;
+        LAUNCH(m->dev, tf32_lo_kernel, grid_for(n4, 256, m->dev->sm_count), 256, 0,
+               reinterpret_cast<const float4 *>(j.src), reinterpret_cast<float4 *>(*j.dst), n4);
+      }
+    }
+  }
   CK(cudaMalloc(reinterpret_cast<void **>(&m->d_layers), lp.size() * sizeof(LayerPtrs)));
   m->allocs.push_back(m->d_layers);
   CK(cudaMemcpyAsync(m->d_layers, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice, m->dev->stream));
@@ -1226,8 +1276,9 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   // s->h already holds the LayerNorm of s->x that the next product wants (left there by the split-K second
   // stage of the product that wrote s->x)
   bool h_ready = false;
-  auto mm = [&](const float *a, const float *gamma, const float *beta, const float *Wt, int K, int N,
-                const Epilogue &e, const float *next_gamma = nullptr, const float *next_beta = nullptr) -> int32_t {
+  auto mm = [&](const float *a, const float *gamma, const float *beta, const float *Wt, const float *Wt_lo, int K,
+                int N, const Epilogue &e, const float *next_gamma = nullptr, const float *next_beta = nullptr,
+                SplitHandoff *handoff = nullptr) -> int32_t {
     // a: [M,K] contiguous. Small M: weight-streaming GEMV with the LayerNorm fused in; otherwise a LayerNorm pass
     // into s->h (separate, or riding on the previous product's second stage) and a tiled GEMM. next_gamma/beta:
     // the LayerNorm that will consume this product's output rows e.out[M,N].
@@ -1241,7 +1292,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     LnAfter ln = {next_gamma, next_beta, s->h, false};
     // the product must not read s->h itself while its second stage rewrites it
     bool can_fuse = next_gamma != nullptr && src != s->h;
-    TRY(launch_gemm_nk(dev, src, (size_t)K, Wt, M, K, N, e, can_fuse ? &ln : nullptr));
+    TRY(launch_gemm_nk(dev, src, (size_t)K, Wt, M, K, N, e, can_fuse ? &ln : nullptr, Wt_lo, handoff));
     h_ready = ln.done;
     return WGPT_OK;
   };
@@ -1249,12 +1300,20 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   for (int l = 0; l < p.n_layer; l++) {
     const LayerWeights &L = m->layers[l];
     float *kc = s->kc + (size_t)l * kv_layer, *vc = s->vc + (size_t)l * kv_layer;
+    SplitHandoff qkv_slices;
     {  // LN1 + QKV projection; K and V rows go straight into the cache
       Epilogue e = plain_epi(s->q, E, L.bqkv);
       e.kc = kc; e.vc = vc; e.E = E; e.n_tok = n_tok; e.n_ctx = p.n_ctx; e.pos = s->d_pos;
-      TRY(mm(s->x, L.ln1_g, L.ln1_b, L.wqkv_t, E, 3 * E, e));
+      // one query per sequence and one position slice: the attention CTAs can add the product's slices themselves
+      const bool consumer_sums = n_tok == 1 && s->n_split == 1 && 3 * hs <= 256;
+      TRY(mm(s->x, L.ln1_g, L.ln1_b, L.wqkv_t, L.wqkv_lo, E, 3 * E, e, nullptr, nullptr,
+             consumer_sums ? &qkv_slices : nullptr));
     }
-    if (n_tok == 1)
+    if (n_tok == 1 && qkv_slices.taken) {
+      QkvPartials qp{qkv_slices.part, L.bqkv, qkv_slices.splits, M, E};
+      TRY(launch_attn_decode(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, s->n_seq, H, s->n_split, s->d_pos,
+                             m->scale, s->attn_part, &qp));
+    } else if (n_tok == 1)
       TRY(launch_attn_decode(dev, hs, s->q, E, kc, vc, E, (size_t)p.n_ctx, s->o, E, s->n_seq, H, s->n_split, s->d_pos,
                              m->scale, s->attn_part));
     else
@@ -1272,16 +1331,16 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
         } else {
           dim3 mg((E / 4 + 127) / 128, M);
           LAUNCH_PDL(dev, attn_merge_kernel, mg, 128, 0, ap, s->o, E);
-          TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e, L.ln2_g, L.ln2_b));
+          TRY(mm(s->o, nullptr, nullptr, L.wo_t, L.wo_lo, E, E, e, L.ln2_g, L.ln2_b));
         }
       } else {
-        TRY(mm(s->o, nullptr, nullptr, L.wo_t, E, E, e, L.ln2_g, L.ln2_b));
+        TRY(mm(s->o, nullptr, nullptr, L.wo_t, L.wo_lo, E, E, e, L.ln2_g, L.ln2_b));
       }
     }
     {  // LN2 + MLP up-projection + GELU
       Epilogue e = plain_epi(s->f, F, L.bfc);
       e.act = 1;
-      TRY(mm(s->x, L.ln2_g, L.ln2_b, L.wfc_t, E, F, e));
+      TRY(mm(s->x, L.ln2_g, L.ln2_b, L.wfc_t, L.wfc_lo, E, F, e));
     }
     {  // MLP down-projection + residual
       Epilogue e = plain_epi(s->x, E, L.bpr);
@@ -1290,7 +1349,7 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
       // the next consumer of s->x: the following block's ln_1, or ln_f when every row is a newest row
       const float *ng = last ? (n_tok == 1 ? m->lnf_g : nullptr) : m->layers[l + 1].ln1_g;
       const float *nb = last ? (n_tok == 1 ? m->lnf_b : nullptr) : m->layers[l + 1].ln1_b;
-      TRY(mm(s->f, nullptr, nullptr, L.wpr_t, F, E, e, ng, nb));
+      TRY(mm(s->f, nullptr, nullptr, L.wpr_t, L.wpr_lo, F, E, e, ng, nb));
     }
   }
   // ln_f + tied de-embedding on the newest row of each sequence only (the reference normalises all rows and

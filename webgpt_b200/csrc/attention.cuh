@@ -19,11 +19,21 @@ namespace wgpt {
 // HBM-bound: reads 2*HS*4 bytes per position per head. Before the dependency wait the CTA asks for its slice of
 // the cache in L2, computed from the position counter as it stands then (possibly one step old: the rows of
 // earlier positions never change, so a stale bound only misses the newest row).
-template <int HS>
+// Split-K partial tiles of the QKV product that feeds a decode attention (batched decode on the tensor cores):
+// [slice][feature tile of 128][row = sequence][128], feature n of [0, 3E) = q | k | v. With FROM_QKV_PART the
+// attention CTA is that product's second stage for its own (sequence, head): it adds the slices in order, adds the
+// bias, keeps q, and writes the k and v rows of the newest position into the cache before it reads the cache.
+struct QkvPartials {
+  const float *part;
+  const float *bias;  // [3E]
+  int splits, n_rows, E;
+};
+
+template <int HS, bool FROM_QKV_PART = false>
 __global__ void __launch_bounds__(256)
 attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc, const float *__restrict__ vc,
                    int ldkv, size_t kv_seq_stride, float *__restrict__ out, int ldo, const int *__restrict__ pos,
-                   float scale, float *__restrict__ part) {
+                   float scale, float *__restrict__ part, QkvPartials qp = QkvPartials()) {
   constexpr int LPP = HS / 4;      // lanes per position (one float4 each)
   constexpr int G = 32 / LPP;      // positions per warp iteration
   constexpr int NW = 8;
@@ -47,7 +57,29 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
   const int L = __ldcg(pos) + 1;
   const int chunk = (L + n_split - 1) / n_split;
   const int beg = split * chunk, end = min(L, beg + chunk);
-  const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4));
+  float4 q4;
+  if (FROM_QKV_PART) {
+    __shared__ __align__(16) float s_q[HS];
+    if (tid < 3 * HS) {
+      const int sec = tid / HS, d = tid - sec * HS;
+      const int n = sec * qp.E + h * HS + d;
+      const int n_tiles = (3 * qp.E + 127) >> 7, nt = n >> 7;
+      const float *p0 = qp.part + ((size_t)nt * qp.n_rows + seq) * 128 + (n & 127);
+      const size_t zstride = (size_t)n_tiles * qp.n_rows * 128;
+      float a = 0.f;
+#pragma unroll 8
+      for (int z = 0; z < qp.splits; z++) a += __ldcg(p0 + (size_t)z * zstride);
+      a += qp.bias[n];
+      if (sec == 0) s_q[d] = a;
+      // the newest position's row; kc/vc are written here and read below by this same CTA only
+      else if (sec == 1) const_cast<float *>(kb)[(size_t)(L - 1) * ldkv + d] = a;
+      else const_cast<float *>(vb)[(size_t)(L - 1) * ldkv + d] = a;
+    }
+    __syncthreads();
+    q4 = *reinterpret_cast<const float4 *>(&s_q[lig * 4]);
+  } else {
+    q4 = __ldcg(reinterpret_cast<const float4 *>(q + (size_t)seq * ldq + h * HS + lig * 4));
+  }
   kb += lig * 4;
   vb += lig * 4;
 

@@ -172,6 +172,21 @@ __global__ void argmax_kernel(const float *__restrict__ logits, int V, uint32_t 
   }
 }
 
+// lo = w - tf32(w): what a TF32 tensor-core product drops from each weight (it reads the top 19 bits of an FP32
+// operand), kept as a second matrix so that the 3xTF32 GEMM can fetch it by TMA. Load time only.
+__global__ void tf32_lo_kernel(const float4 *__restrict__ w, float4 *__restrict__ lo, size_t n4) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    float4 x = w[i], l;
+    l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+    l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+    l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+    l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+    lo[i] = l;
+  }
+}
+
 // Advances the session's device-side position and step counters after a decode step.
 __global__ void advance_kernel(int *pos, int *step, int n_tok) {
   pdl_wait();

@@ -144,9 +144,9 @@ __device__ __forceinline__ TcWork tc_work(int w, int m_tiles, int n_tiles, int k
 // Two accumulators in tensor memory alternate, so the epilogue of one tile overlaps the main loop of the next.
 template <bool X3>
 __global__ void __launch_bounds__(TcPlan<X3>::kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int M, int K,
-               int N, Epilogue epi, int *err, int kb_per_split, int splits, float *split_out, int static_op,
-               int transposed) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_b_lo, int M, int K, int N, Epilogue epi, int *err,
+               int kb_per_split, int splits, float *split_out, int static_op, int transposed, int b_lo_tma) {
   using Plan = TcPlan<X3>;
   constexpr int S = Plan::kStages;
   extern __shared__ uint8_t tc_smem_raw[];
@@ -163,6 +163,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + TC_BN - 1) / TC_BN;
   const int n_work = m_tiles * n_tiles * splits;
+  // 3xTF32 with the weight operand's low part precomputed in HBM (map_b_lo): TMA brings it into the stage's B-lo
+  // slot and the split warps only treat the A tile. Requires B to be the static operand or no early loads.
+  const bool lo_tma = X3 && b_lo_tma != 0;
 #ifdef WGPT_TRACE
   __shared__ unsigned int tc_trace_base;  // the roles below are different threads: they share thread 0's record
   {
@@ -206,10 +209,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pre = t.num_kb < S ? t.num_kb : S;
     for (int kb = 0; kb < pre; kb++) {
       uint8_t *st = tiles + (size_t)kb * Plan::kStageBytes;
-      mbar_expect_tx(&full[kb], 2 * TC_TILE_BYTES);
-      if (static_op == 1)
+      mbar_expect_tx(&full[kb], (lo_tma ? 3 : 2) * TC_TILE_BYTES);
+      if (static_op == 1) {
         tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[kb]);
-      else
+        if (lo_tma) tma_load_2d(st + 3 * TC_TILE_BYTES, &map_b_lo, (t.kb0 + kb) * TC_BK, t.n0, &full[kb]);
+      } else
         tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[kb]);
     }
   }
@@ -233,9 +237,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             continue;
           }
           if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
-          mbar_expect_tx(&full[s], 2 * TC_TILE_BYTES);
+          mbar_expect_tx(&full[s], (lo_tma ? 3 : 2) * TC_TILE_BYTES);
           tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[s]);
           tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
+          if (lo_tma) tma_load_2d(st + 3 * TC_TILE_BYTES, &map_b_lo, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
         }
         if (w == blockIdx.x) TC_TRACE(3);
       }
@@ -397,6 +402,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lo = hi + 2 * TC_TILE_BYTES;
 #pragma unroll 8
         for (int q = 0; q < (2 * TC_TILE_BYTES) / (16 * 128); q++) {
+          if (lo_tma && q == TC_TILE_BYTES / (16 * 128)) break;  // the B tile's low part came by TMA
           // kind::tf32 reads the top 19 bits of each FP32 operand and ignores the rest (checked on B200: clearing
           // the low 13 bits first gives bit-identical products), so the staged tile itself serves as `hi`.
           float4 x = lds128(hi + (uint32_t)q * 2048u), l;
