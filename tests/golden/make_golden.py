@@ -82,8 +82,39 @@ def make_attention_kat():
     np.savez_compressed(os.path.join(HERE, "attention_kat.npz"), P=P, V=V, expected=expected, H=H)
 
 
+def make_sampling_kat():
+    """Known answers of the sampling step (model.js:81-83) from the Python mirror of globals.js:47-74, which is
+    written independently of the C oracle: rows of logits (distinct values, heavy ties with +0/-0, all equal),
+    several top_k / temperature / uniform numbers each, the kept indices in order and the pick."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from webgpt_b200 import globals as G
+    rng = np.random.default_rng(2024)
+    V = 777
+    rows = [
+        (rng.standard_normal(V) * 4 - 30).astype(np.float32),
+        (rng.standard_normal(V) * 4 + 10).astype(np.float32),
+        np.round(rng.standard_normal(V) * 2).astype(np.float32),
+        np.zeros(V, np.float32),
+    ]
+    rows[2][rows[2] == 0] *= rng.choice([-1.0, 1.0], size=int((rows[2] == 0).sum())).astype(np.float32)
+    rows[3][1::2] = -0.0
+    cases = []
+    for ri, logits in enumerate(rows):
+        for top_k in (1, 2, 3, 40, 100, 128):
+            for temperature in (0.3, 1.0, 1.7):
+                for u in (0.0, float(rng.random()), float(rng.random()), 0.9999999999):
+                    sel = G.selectTopK(logits, top_k)
+                    probs = G.cpuSoftmax(sel["topKProbs"], temperature)
+                    pick = sel["topKIndices"][G.sampleFromDistribution(probs, u)]
+                    cases.append((ri, top_k, temperature, u, pick))
+    c = np.array(cases, np.float64)
+    np.savez_compressed(os.path.join(HERE, "sampling_kat.npz"), logits=np.stack(rows), row=c[:, 0].astype(np.int32),
+                        top_k=c[:, 1].astype(np.int32), temperature=c[:, 2], u=c[:, 3], pick=c[:, 4].astype(np.int32))
+
+
 if __name__ == "__main__":
     make_attention_kat()
+    make_sampling_kat()
     # std is larger than the benchmark's 0.02 so that greedy decoding does not collapse onto one token
     # window stays inside n_ctx
     make_gpt2_case("gpt2_tiny.npz", "tiny", n_prompt=5, n_new=8, seed=101, ln_random=True, std=0.2)

@@ -137,3 +137,16 @@ def test_gpt_generate_routes_agree(oracle):
         finally:
             gpt.destroy()
     assert outs[0] == outs[1]
+
+
+def test_sample_topk_golden(dev):
+    """Device picks against the committed known answers (made from the Python mirror of globals.js:47-74,
+    independent of the C oracle)."""
+    from conftest import load_golden
+    g = load_golden("sampling_kat.npz")
+    keys = sorted({(int(k), float(t)) for k, t in zip(g["top_k"], g["temperature"])})
+    for k, t in keys:
+        sel = [i for i in range(len(g["pick"])) if int(g["top_k"][i]) == k and float(g["temperature"][i]) == t]
+        rows = g["logits"][g["row"][sel]]
+        got = device_picks(dev, rows, k, t, g["u"][sel])
+        assert [int(x) for x in got] == [int(x) for x in g["pick"][sel]], (k, t)

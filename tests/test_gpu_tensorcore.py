@@ -144,3 +144,53 @@ def test_batched_decode_gpt2_width(oracle):
                 assert rel_err(lg[i], ref) < 5e-5
     finally:
         gpt.destroy()
+
+
+def test_prefill_8192_rows_gpt2_width(oracle):
+    """The batched configuration's prefill at full row count through the model path: 64 sequences x 128 tokens =
+    8192 rows at GPT-2 width (one layer, small vocabulary), i.e. the persistent 128x128-tile products with the
+    weights' low parts fetched by TMA. Logits of the last position of sampled sequences against the oracle."""
+    from webgpt_b200 import GPT
+    params = dict(n_layer=1, n_head=12, n_embd=768, n_ctx=136, vocab_size=512)
+    w = synth.make_weights(params, seed=33, std=0.05, ln_random=True)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    gpt = GPT(None, params=params, weights=w)
+    gpt.initialize()
+    try:
+        n_seq, n_tok = 64, 128
+        prompts = np.stack([synth.make_tokens(params["vocab_size"], n_tok, seed=60, stream=i) for i in range(n_seq)])
+        s = gpt.session(n_seq)
+        s.reset()
+        lg = s.forward(prompts)
+        for i in (0, 17, n_seq - 1):
+            assert rel_err(lg[i], m.run(prompts[i])) < 5e-5, i
+        s.reset()
+        assert np.array_equal(s.forward(prompts), lg)  # bit-identical repeat
+    finally:
+        gpt.destroy()
+
+
+def test_batched_decode_xl_width(oracle):
+    """GPT-2 XL width (d = 1600, 25 heads of 64) cut to two layers, 16 sequences decoded together: 1600 and 4800
+    are not multiples of the 128-wide feature tile, so the last tile of every split-K product is ragged and the
+    q | k | v boundaries fall inside tiles."""
+    from webgpt_b200 import GPT
+    params = dict(n_layer=2, n_head=25, n_embd=1600, n_ctx=32, vocab_size=512)
+    w = synth.make_weights(params, seed=35, std=0.04, ln_random=True)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    gpt = GPT(None, params=params, weights=w)
+    gpt.initialize()
+    try:
+        n_seq = 16
+        prompts = np.stack([synth.make_tokens(params["vocab_size"], 6, seed=70, stream=i) for i in range(n_seq)])
+        batch = gpt.session(n_seq).generate_greedy(prompts, 8)
+        for i in (0, 7, n_seq - 1):
+            assert np.array_equal(batch[i], m.kv_generate_greedy(prompts[i], 8)), i
+        s = gpt.session(n_seq)
+        s.reset()
+        s.forward(prompts, want_logits=False)
+        lg = s.forward(batch[:, :1])
+        for i in (2, n_seq - 1):
+            assert rel_err(lg[i], m.run(np.concatenate([prompts[i], batch[i, :1]]))) < 5e-5
+    finally:
+        gpt.destroy()

@@ -227,3 +227,11 @@ def test_sampled_generation_kv_equals_recompute(oracle):
     assert len(set(int(t) for t in a)) > 1
     # top_k = 1 ignores the random numbers and equals the greedy loop
     assert np.array_equal(m.kv_generate_sample(prompt, n_new, 1, 0.8, u), m.kv_generate_greedy(prompt, n_new))
+
+
+def test_sample_topk_golden(oracle):
+    """The committed sampling known answers (tests/golden/sampling_kat.npz, made by make_golden.py from the Python
+    mirror of globals.js:47-74) against the C restatement."""
+    g = load_golden("sampling_kat.npz")
+    for r, k, t, u, pick in zip(g["row"], g["top_k"], g["temperature"], g["u"], g["pick"]):
+        assert oracle.sample_topk(g["logits"][r], int(k), float(t), float(u)) == int(pick)

@@ -554,6 +554,10 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
     int want = (dev->sm_count + tiles - 1) / tiles;
     if (want > total_kb / 2) want = total_kb / 2;  // at least two k-blocks per slice: fewer slices to add up
     if (want < 1) want = 1;
+    {
+      static const int max_splits = [] { const char *ev = getenv("WGPT_MAX_SPLITS"); return ev ? atoi(ev) : 0; }();
+      if (max_splits > 0 && want > max_splits) want = max_splits;
+    }
     kb_per_split = (total_kb + want - 1) / want;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
     const size_t n_pad = (size_t)((N + TC_BM - 1) / TC_BM) * TC_BM;  // the exchanged form stores whole feature tiles
