@@ -500,7 +500,7 @@ __global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit
   const int n_tiles = (N + tw - 1) / tw, nt = n / tw;
   const float *p0 = part + ((size_t)nt * M + m) * tw + (n - nt * tw);
   const size_t zstride = (size_t)n_tiles * M * tw;
-#pragma unroll 4
+#pragma unroll 8
   for (int k = 0; k < ksplit; k++) {
     float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
