@@ -194,3 +194,49 @@ def test_batched_decode_xl_width(oracle):
             assert rel_err(lg[i], m.run(np.concatenate([prompts[i], batch[i, :1]]))) < 5e-5
     finally:
         gpt.destroy()
+
+
+PAIR_SCRIPT = r"""
+import numpy as np, sys
+from webgpt_b200 import Device, _lib
+dev = Device(0)
+rng = np.random.default_rng(3)
+worst = 0.0
+for (M, K, N) in [(8192, 768, 2304), (1000, 100, 520), (4100, 64, 2312), (2048, 3072, 3072)]:
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    Wt = (rng.standard_normal((N, K), dtype=np.float32) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N, dtype=np.float32)
+    rows = rng.choice(M, 64, replace=False)
+    ref = A[rows].astype(np.float64) @ Wt.astype(np.float64).T + b
+    Ai = rng.integers(-3, 4, (M, K)).astype(np.float32)
+    Wi = rng.integers(-3, 4, (N, K)).astype(np.float32)
+    refi = Ai[rows].astype(np.float64) @ Wi.astype(np.float64).T
+    for mode, tol in ((_lib.PRECISION_TF32X3, 5e-5), (_lib.PRECISION_TF32, 3e-3)):
+        dev.set_precision(mode)
+        outs = []
+        for (a, w, bias) in ((A, Wt, b), (Ai, Wi, np.zeros(N, np.float32))):
+            a_d, w_d, b_d, o_d = dev.tensor(a), dev.tensor(w), dev.tensor(bias), dev.buffer(M * N * 4)
+            _lib.call("wgpt_matmul_nk", dev.handle, M, N, K, a_d.ptr, w_d.ptr, b_d.ptr, o_d.ptr)
+            _lib.call("wgpt_device_check", dev.handle)
+            outs.append(o_d.read(np.float32, M * N).reshape(M, N))
+            for buf in (a_d, w_d, b_d, o_d): buf.destroy()
+        err = float(np.max(np.abs(outs[0][rows] - ref)) / np.max(np.abs(ref)))
+        assert err < tol, (M, K, N, mode, err)
+        assert np.array_equal(outs[1][rows].astype(np.float64), refi), (M, K, N, mode)
+        worst = max(worst, err)
+print("PAIR_OK", worst)
+"""
+
+
+def test_pair_gemm_all_shapes():
+    """The CTA-pair kernel (two SMs on one 256 x 256 tile) forced on for every product that fits it, TF32 and
+    3xTF32, including ragged tiles: integer operands must come out exact, random ones within the mode's tolerance.
+    The switch is read once per process, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, WGPT_PAIR_GEMM="2", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", PAIR_SCRIPT], env=env, cwd=root, capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0 and "PAIR_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

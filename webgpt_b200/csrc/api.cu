@@ -18,6 +18,7 @@
 #include "decode_persistent.cuh"
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "int8.cuh"
 #include "sampling.cuh"
 #include "matmul.cuh"
@@ -585,6 +586,34 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   const bool lo_tma = x3 && Wt_lo != nullptr && !exchanged && b_static;
   CUtensorMap mlo = mb;
   if (lo_tma) TRY(make_tile_map(&mlo, Wt_lo, (uint64_t)N, (uint64_t)K, (uint64_t)K));
+  // Large 3xTF32 products without split-K and without a precomputed low part of the weight (the per-operator
+  // entry points) run on the CTA-pair kernel (256 x 256 tile per two SMs) when its tiles fill the pairs evenly
+  // enough. Measured back to back: 8192x768x2304 226-232 against 171-182 TFLOP/s; with 96 tiles on 74 pairs it is
+  // no faster than the 128 x 128 tiles, in plain TF32 it is slower (302 against 330-360), and inside the model's
+  // prefill the one-CTA kernel with the low part fetched by TMA measured the same or better (10.9 against 11.1 ms),
+  // so the model path keeps that. WGPT_PAIR_GEMM=0 turns the pair kernel off, 2 uses it wherever it fits.
+  static const int pair_mode = [] { const char *ev = getenv("WGPT_PAIR_GEMM"); return ev ? atoi(ev) : 1; }();
+  const int work2 = ((M + 255) / 256) * ((N + TC2_BN - 1) / TC2_BN);
+  int pairs = dev->sm_count / 2;
+  const int rounds2 = (work2 + pairs - 1) / pairs;
+  const bool pair_fits = work2 * 5 >= rounds2 * pairs * 4;  // at least 80 % of the pair slots do useful work
+  if (pair_mode > 0 && ((x3 && !lo_tma) || pair_mode == 2) && split_out == nullptr && !exchanged && M >= 512 &&
+      N >= 256 && pair_fits) {
+    if (pairs > work2) pairs = work2;
+    dim3 grid2(2 * pairs);
+    if (x3) {
+      auto kern = gemm_tc2_kernel<true>;
+      CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
+      LAUNCH_PDL(dev, kern, grid2, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, ma, mb, mlo, M, K, N, epi,
+                 dev->d_err, lo_tma ? 1 : 0);
+    } else {
+      auto kern = gemm_tc2_kernel<false>;
+      CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
+      LAUNCH_PDL(dev, kern, grid2, TcPlan<false>::kThreads, TcPlan<false>::kSmemBytes, ma, mb, mlo, M, K, N, epi,
+                 dev->d_err, 0);
+    }
+    return WGPT_OK;
+  }
   if (x3) {
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
