@@ -22,7 +22,8 @@ struct Epilogue {
   // lands in cache row seq*n_ctx + *pos + t.
   float *kc, *vc;
   int E, n_tok, n_ctx;
-  const int *pos;
+  const int *pos;  // device position counter; a kernel that stores many elements reads it once into pos_base
+  int pos_base;    // used when pos == nullptr
 };
 
 __device__ __forceinline__ float gelu_f(float x) {
@@ -39,7 +40,7 @@ __device__ __forceinline__ float *epi_addr(const Epilogue &e, int m, int n) {
   int sec = n >= 2 * e.E ? 2 : 1;
   int c = n - sec * e.E;
   int seq = m / e.n_tok, t = m - seq * e.n_tok;
-  size_t row = (size_t)seq * e.n_ctx + (size_t)__ldcg(e.pos) + t;
+  size_t row = (size_t)seq * e.n_ctx + (size_t)(e.pos ? __ldcg(e.pos) : e.pos_base) + t;
   return (sec == 1 ? e.kc : e.vc) + row * e.E + c;
 }
 

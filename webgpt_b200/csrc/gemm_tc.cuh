@@ -294,6 +294,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after();
       if (i == 0 && warp == 2) TC_TRACE(6);
       Epilogue e = epi;
+      if (e.kc != nullptr && e.pos != nullptr) {  // one read of the position counter instead of one per store
+        e.pos_base = __ldcg(e.pos);
+        e.pos = nullptr;
+      }
       if (split_out != nullptr) {  // raw partial tile of K slice z; a second kernel sums the slices in order
         e.colscale = nullptr; e.bias = nullptr; e.residual = nullptr; e.kc = nullptr; e.vc = nullptr;
         e.act = 0;

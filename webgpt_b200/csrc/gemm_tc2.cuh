@@ -200,6 +200,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int quad = warp & 3;
     float *pad = epi_pad + (warp - 2) * (32 * 33);
     const int sub_r = lane >> 3, col4 = (lane & 7) * 4;
+    Epilogue e = epi;
+    if (e.kc != nullptr && e.pos != nullptr) {  // one read of the position counter instead of one per store
+      e.pos_base = __ldcg(e.pos);
+      e.pos = nullptr;
+    }
     int i = 0;
     for (int w = pair; w < n_work; w += pairs, i++) {
       const int nt = w / m_tiles, mt = w - nt * m_tiles;
@@ -211,7 +216,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TC2_BN);
       const int row0 = m0 + quad * 32;
       const bool rows_live = row0 < M;
-      const bool vec_ok = ((N | epi.ld) & 3) == 0;
+      const bool vec_ok = ((N | e.ld) & 3) == 0;
 #pragma unroll 1
       for (int c = 0; c < TC2_BN / 32; c++) {
         float v[32];
@@ -234,12 +239,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const float4 x = make_float4(src[0], src[1], src[2], src[3]);
           if (m < M && n < N) {
             if (vec_ok) {
-              epi_store4(epi, x, m, n);
+              epi_store4(e, x, m, n);
             } else {
-              epi_store(epi, x.x, m, n);
-              if (n + 1 < N) epi_store(epi, x.y, m, n + 1);
-              if (n + 2 < N) epi_store(epi, x.z, m, n + 2);
-              if (n + 3 < N) epi_store(epi, x.w, m, n + 3);
+              epi_store(e, x.x, m, n);
+              if (n + 1 < N) epi_store(e, x.y, m, n + 1);
+              if (n + 2 < N) epi_store(e, x.z, m, n + 2);
+              if (n + 3 < N) epi_store(e, x.w, m, n + 3);
             }
           }
         }
