@@ -65,6 +65,16 @@ __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
                : "memory");
 }
 
+// TMA tile load whose completion is counted on an mbarrier given by shared::cluster address, which may belong to
+// the other CTA of the pair (cta_group::2 form, no multicast); the tile itself lands in this CTA's shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_addr)
+      : "memory");
+}
+
 // gridDim.x = 2 x pairs, cluster (2,1,1). Pair p walks the 256 x 256 tiles p, p + pairs, ... (row tile fastest).
 template <bool X3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TcPlan<X3>::kThreads, 1)
@@ -128,6 +138,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int s = kc % S, it = kc / S;
           uint8_t *st = tiles + (size_t)s * Plan::kStageBytes;
           if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
+          if (!X3) {
+            // plain TF32: nothing in this CTA looks at the staged tiles, so both CTAs' loads are counted on the
+            // leader's barrier (which expects the bytes of both) and no relay is needed
+            const uint32_t lead_full = peer_smem_addr(&full[s], 0);
+            if (leader) mbar_expect_tx(&full[s], 4 * TC_TILE_BYTES);
+            tma_load_2d_pair(st, &map_a, kb * TC_BK, m0, lead_full);
+            tma_load_2d_pair(st + TC_TILE_BYTES, &map_b, kb * TC_BK, nb0, lead_full);
+            continue;
+          }
           mbar_expect_tx(&full[s], (lo_tma ? 3 : 2) * TC_TILE_BYTES);
           tma_load_2d(st, &map_a, kb * TC_BK, m0, &full[s]);
           tma_load_2d(st + TC_TILE_BYTES, &map_b, kb * TC_BK, nb0, &full[s]);
@@ -148,7 +167,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int kb = 0; kb < total_kb; kb++, kc++) {
           const int s = kc % S, it = kc / S;
           uint64_t *go = X3 ? &ready[s] : &full[s];
-          if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS) || !mbar_wait(&peer_ready[s], it & 1, TC_POLLS)) {
+          if (*abort_flag || !mbar_wait(go, it & 1, TC_POLLS) ||
+              (X3 && !mbar_wait(&peer_ready[s], it & 1, TC_POLLS))) {
             *abort_flag = 1;
             break;
           }
@@ -172,7 +192,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         umma2_commit(smem_addr(&acc_full[buf]));  // (also reached after an abort)
         umma2_commit(peer_smem_addr(&acc_full[buf], 1));
       }
-    } else if (!leader && lane < S) {
+    } else if (X3 && !leader && lane < S) {
       // ---------------- stage relays (the other CTA): lane s tells the leader each time stage s of this CTA is
       // ready (tiles landed; in 3 x TF32 also the low parts written). A remote arrive occupies its thread for about
       // a microsecond, so one lane per stage keeps S of them in flight ----------------
