@@ -13,7 +13,7 @@
 //     accumulator buffers (peer_acc_empty);
 //   * the leader's tcgen05.commit arrives on the empty / acc_full barriers of both CTAs (one commit per CTA,
 //     the second through the other CTA's shared-memory address).
-// No TMA or commit multicast is used. Every wait is bounded; on expiry the CTA sets *err = 3, drains and exits.
+// Every load and every commit names exactly one destination CTA. Every wait is bounded; on expiry the CTA sets *err = 3, drains and exits.
 #pragma once
 #include "gemm_tc.cuh"
 
@@ -66,7 +66,7 @@ __device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
 }
 
 // TMA tile load whose completion is counted on an mbarrier given by shared::cluster address, which may belong to
-// the other CTA of the pair (cta_group::2 form, no multicast); the tile itself lands in this CTA's shared memory.
+// the other CTA of the pair (cta_group::2 form, one destination); the tile itself lands in this CTA's shared memory.
 __device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_addr) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
