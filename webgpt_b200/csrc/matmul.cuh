@@ -540,12 +540,19 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
       const size_t zstride = (size_t)n_tiles * M * tw;
       // eight slices in flight per thread: the row is short and few CTAs run, so the loop is bound by latency
       int k = 0;
-      for (; k + 8 <= ksplit; k += 8) {
-        float4 t[8];
+      for (; k + 12 <= ksplit; k += 12) {
+        float4 t[12];
 #pragma unroll
-        for (int u = 0; u < 8; u++) t[u] = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(k + u) * zstride));
+        for (int u = 0; u < 12; u++) t[u] = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(k + u) * zstride));
 #pragma unroll
-        for (int u = 0; u < 8; u++) { a.x += t[u].x; a.y += t[u].y; a.z += t[u].z; a.w += t[u].w; }
+        for (int u = 0; u < 12; u++) { a.x += t[u].x; a.y += t[u].y; a.z += t[u].z; a.w += t[u].w; }
+      }
+      for (; k + 4 <= ksplit; k += 4) {
+        float4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) t[u] = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(k + u) * zstride));
+#pragma unroll
+        for (int u = 0; u < 4; u++) { a.x += t[u].x; a.y += t[u].y; a.z += t[u].z; a.w += t[u].w; }
       }
       for (; k < ksplit; k++) {
         float4 t = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
