@@ -68,6 +68,9 @@ int32_t wgpt_device_synchronize(wgpt_device *dev);
 int32_t wgpt_device_set_precision(wgpt_device *dev, int32_t mode);
 /* Number of kernels this library has launched on the device since creation. */
 int32_t wgpt_device_launch_count(wgpt_device *dev, uint64_t *count);
+/* Free and total device memory in bytes as the driver reports them (the reference reads its budget from
+ * device.limits, instructions.js:75-80). Lets a caller check that a call allocated nothing. */
+int32_t wgpt_device_mem_info(wgpt_device *dev, uint64_t *free_bytes, uint64_t *total_bytes);
 
 /* ---- buffers: Block.initBuffer / GPT.initTensor (instructions.js:67-81, model.js:490-500),
  *      queue copies (model.js:253-255), mapAsync read-back (model.js:261-263). */
@@ -131,11 +134,13 @@ int32_t wgpt_device_check(wgpt_device *dev);
  * grow a library-owned workspace for its split-K partial sums; this entry point keeps them in an array compiled
  * into the library (WGPT_STATIC_SCRATCH_FLOATS floats = 8 MiB per GPU that loads the library, held until
  * exit) and calls no allocating routine.
- *  - Limits: rows <= 8 and rows * cols <= WGPT_STATIC_SCRATCH_FLOATS, otherwise WGPT_ERR_SHAPE; all other
- *    preconditions are those of wgpt_matmul. When the usual K split does not fit the array a smaller split is
- *    used, so results may differ from wgpt_matmul in the last bits (different summation order).
+ *  - Limits: rows <= 8 and (K slices) * rows * cols <= WGPT_STATIC_SCRATCH_FLOATS, otherwise WGPT_ERR_SHAPE
+ *    (rows * cols above the array size is always refused; the K split is the one wgpt_matmul uses, a few hundred
+ *    slices at most for very long shared dimensions). All other preconditions are those of wgpt_matmul.
  *  - The first call on each device looks up the array's device address; make that first call outside any
- *    stream capture.
+ *    stream capture. The CUDA runtime loads a library's device code, this array included, when the library is
+ *    first used on a GPU, and that load takes device memory: the "allocates nothing" guarantee holds from the
+ *    second call on (make one warm-up call per GPU at start-up).
  *  - All calls on one GPU share the array (it keeps the previous call's partial sums; every call overwrites all
  *    it reads, nothing needs clearing). Calls on the same wgpt_device are stream-ordered and safe; calls that
  *    can overlap on one GPU (two wgpt_device handles on the same ordinal) race on it. */

@@ -65,31 +65,98 @@ def test_kv_cached_steps_equal_recompute(oracle):
         gpt.destroy()
 
 
-def test_kv_slot_indexing_exact():
-    """Index-encoding pattern: with zeroed attention/MLP weights and identity-free paths the K/V rows written to
-    the cache depend only on (token, position); feeding the same tokens in different chunkings must leave
-    bit-identical logits, and a reset must forget everything."""
-    params = synth.CONFIGS["small"]
-    w = synth.make_weights(params, seed=5, std=0.1, ln_random=True)
+def _walsh(n):
+    h = np.array([[1]], np.int64)
+    while h.shape[0] < n:
+        h = np.block([[h, h], [h, -h]])
+    return h
+
+
+def kv_index_pattern():
+    """A one-layer model whose arithmetic is exact in f32 whatever the summation order, built so that the residual
+    stream after the block spells out which cache rows each head read.
+
+    E = 128 in four blocks of 32, four heads of 32. Position t carries the balanced +-1 Walsh code c_t and token id
+    the code d_id: x_t = 16 * [c_t, c_t, d_id, d_id]. Such a row has mean 0 and variance 256 exactly, and
+    256 + 1e-5 rounds to 256 in f32, so ln_1 (gamma 1, beta 0) gives exactly x_t / 16, whether a kernel divides by
+    the deviation or multiplies by its reciprocal. The query of head 0 is 64 * c_(t-1), of head 1 64 * c_(t//2), of
+    head 2 64 * c_0, of head 3 64 * c_t; keys are c_j: the matching key scores 2048 / sqrt(32), every other visible
+    key 0, and exp(-362) is exactly 0, so each head's softmax is exactly one-hot. Values are c_j (heads 0, 3) and
+    d_id_j (heads 1, 2); the output projection is the identity; ln_2 has gamma = beta = 0 and the MLP weights are
+    zero, so the block adds exactly the selected value rows: small integers everywhere, TF32-exact as well."""
+    E, H, hs, n_ctx, V = 128, 4, 32, 32, 64
+    params = dict(n_layer=1, n_head=H, n_embd=E, n_ctx=n_ctx, vocab_size=V)
+    W = _walsh(32)[1:]                       # 31 balanced, mutually orthogonal rows
+    c = lambda t: W[t % 31]
+    d = lambda i: W[(7 * i + 3) % 31]
+    z = np.zeros(32, np.int64)
+    wte = np.stack([16 * np.concatenate([z, z, d(i), d(i)]) for i in range(V)])
+    wpe = np.stack([16 * np.concatenate([c(t), c(t), z, z]) for t in range(n_ctx)])
+    sel = [lambda t: max(t - 1, 0), lambda t: t // 2, lambda t: 0, lambda t: t]
+    # M_f c_t = c_f(t): sum over t of outer(c_f(t), c_t) / 32; times 64 the entries are even integers
+    def qmap(f):
+        return sum(np.outer(c(f(t)), c(t)) for t in range(31)) * 2   # = 64 * M_f
+    wq = np.zeros((E, E), np.int64)
+    wk = np.zeros((E, E), np.int64)
+    wv = np.zeros((E, E), np.int64)
+    I = np.eye(32, dtype=np.int64)
+    for hd in range(4):
+        o = slice(32 * hd, 32 * hd + 32)
+        wq[0:32, o] = qmap(sel[hd]).T      # q = h . Wq reads the position code of block 0
+        wk[0:32, o] = I
+        wv[(0 if hd in (0, 3) else 64):(32 if hd in (0, 3) else 96), o] = I
+    w = synth.make_weights(params, seed=1, std=0.0)
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    w["transformer.wte.weight"] = f32(wte)
+    w["transformer.wpe.weight"] = f32(wpe)
+    w["transformer.h.0.attn.c_attn.weight"] = f32(np.concatenate([wq, wk, wv], axis=1))
+    w["transformer.h.0.attn.c_proj.weight"] = f32(np.eye(E))
+    w["transformer.h.0.ln_2.weight"] = np.zeros(E, np.float32)
+
+    def expected(ids):
+        x = np.stack([wte[i] + wpe[t] for t, i in enumerate(ids)])
+        out = x.copy()
+        for t in range(len(ids)):
+            for hd in range(4):
+                j = sel[hd](t)
+                val = c(j) if hd in (0, 3) else d(int(ids[j]))
+                out[t, 32 * hd:32 * hd + 32] += val
+        return out.astype(np.float32)
+    return params, w, expected
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32x3"])
+def test_kv_slot_indexing_exact(precision):
+    """KV slot indexing, bit for bit: with the exact index-encoding model above, the residual stream after the
+    block must equal the integer prediction exactly for every row, however the 24 tokens were fed (24 x 1, 1 x 24,
+    5 + 1 + 1 + 17, 23 + 1): row t of the cache depends on (token t, position t) only (positions 0..T-1 of
+    instructions.js:812-819, the [T, E] K/V rows read by :1141-1214). The logits of the newest row must then be
+    bit-identical across chunkings as well."""
+    from webgpt_b200 import _lib
+    params, w, expected = kv_index_pattern()
     gpt = make_gpt(params, w)
     try:
+        gpt.device.set_precision(_lib.PRECISION_FP32 if precision == "fp32" else _lib.PRECISION_TF32X3)
         ids = synth.make_tokens(params["vocab_size"], 24, seed=3)
+        want = expected(ids)
         s = gpt.session()
-        outs = []
-        for chunks in ([24], [1] * 24, [5, 1, 1, 17], [23, 1]):
+        logits = []
+        for chunks in ([24], [1] * 24, [5, 1, 1, 17], [23, 1], [9, 15]):
             s.reset()
             pos = 0
             for c in chunks:
                 lg = s.forward(ids[pos:pos + c])[0]
+                tap = s.tap()
+                assert tap.shape == (c, params["n_embd"])
+                assert np.array_equal(tap, want[pos:pos + c]), (chunks, pos)
                 pos += c
-            outs.append(lg)
-        for o in outs[1:]:
-            assert rel_err(o, outs[0]) < TIGHT
-        # same chunking twice: bit-identical (no atomics-order dependence anywhere)
+            logits.append(lg)
+        for lg in logits[1:]:
+            assert np.array_equal(lg, logits[0])
+        # a reset forgets everything: token 0 alone reproduces row 0
         s.reset()
-        for t in range(24):
-            lg = s.forward(ids[t:t + 1])[0]
-        assert np.array_equal(lg, outs[1])
+        s.forward(ids[:1])
+        assert np.array_equal(s.tap(), want[:1])
     finally:
         gpt.destroy()
 

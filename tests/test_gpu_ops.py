@@ -206,3 +206,89 @@ def test_pass_list_graph_replay(dev, ops, oracle):
     with pytest.raises(_lib.WgptError) as e:
         _lib.call("wgpt_graph_end", dev.handle, C.byref(g))
     assert e.value.code == _lib.ERR_STATE
+
+
+def test_pass_list_records_embed_layernorm_matmul(oracle):
+    """The reference's pass list starts with the embedding pass (model.js:118); recording embed -> layernorm ->
+    matmul must succeed (the embed call only enqueues while recording) and replay to the eager result. Calls that
+    would synchronise the stream are refused while recording."""
+    import ctypes as C
+    from webgpt_b200 import Device, WgptError, _lib
+    dev = Device(0)
+    try:
+        rng = np.random.default_rng(10)
+        T, E, V, N = 6, 64, 40, 128
+        wte = rng.standard_normal((V, E), dtype=np.float32)
+        wpe = rng.standard_normal((T, E), dtype=np.float32)
+        g, b = rng.standard_normal(E, dtype=np.float32), rng.standard_normal(E, dtype=np.float32)
+        W = (rng.standard_normal((E, N), dtype=np.float32) * 0.1).astype(np.float32)
+        ids = rng.integers(0, V, size=T, dtype=np.uint32)
+        t = dev.tensor
+        ids_d, wte_d, wpe_d, g_d, b_d, w_d = t(ids), t(wte), t(wpe), t(g), t(b), t(W)
+        x_d, h_d, y_d = dev.buffer(T * E * 4), dev.buffer(T * E * 4), dev.buffer(T * N * 4)
+
+        def passes():
+            _lib.call("wgpt_embed", dev.handle, ids_d.ptr, T, E, V, wte_d.ptr, wpe_d.ptr, x_d.ptr)
+            _lib.call("wgpt_layernorm", dev.handle, T, E, x_d.ptr, g_d.ptr, b_d.ptr, h_d.ptr)
+            _lib.call("wgpt_matmul", dev.handle, T, N, E, h_d.ptr, w_d.ptr, None, y_d.ptr)
+
+        passes()
+        eager = y_d.read(np.float32, T * N)
+        ref = oracle.matmul(oracle.layernorm(oracle.embed(ids, wte, wpe), g, b), W)
+        assert rel_err(eager.reshape(T, N), ref) < TOL
+        _lib.call("wgpt_graph_begin", dev.handle)
+        passes()
+        for name, args in (("wgpt_device_synchronize", (dev.handle,)), ("wgpt_device_check", (dev.handle,)),
+                           ("wgpt_buffer_read", (dev.handle, y_d.ptr, 0, eager.ctypes.data, 4)),
+                           ("wgpt_buffer_write", (dev.handle, y_d.ptr, 0, eager.ctypes.data, 4))):
+            with pytest.raises(WgptError) as e:
+                _lib.call(name, *args)
+            assert e.value.code == _lib.ERR_STATE
+        graph = C.c_void_p()
+        _lib.call("wgpt_graph_end", dev.handle, C.byref(graph))
+        y_d.write(np.zeros(T * N, np.float32))
+        _lib.call("wgpt_graph_launch", dev.handle, graph)
+        _lib.call("wgpt_device_check", dev.handle)
+        assert np.array_equal(y_d.read(np.float32, T * N), eager)
+        _lib.call("wgpt_graph_destroy", dev.handle, graph)
+    finally:
+        dev.destroy()
+
+
+def test_stale_pass_list_is_refused_after_workspace_growth():
+    """A recorded pass list holds the address of the library's workspace (split-K partial sums). If a later call
+    makes the workspace grow, the old block is freed; launching the old recording is refused with WGPT_ERR_STATE
+    instead of touching freed memory (the stale recording never runs)."""
+    import ctypes as C
+    from webgpt_b200 import Device, WgptError, _lib
+    dev = Device(0)
+    try:
+        rng = np.random.default_rng(11)
+        A = rng.standard_normal((2, 256), dtype=np.float32)
+        W = rng.standard_normal((256, 128), dtype=np.float32)
+        a_d, w_d, y_d = dev.tensor(A), dev.tensor(W), dev.buffer(2 * 128 * 4)
+        _lib.call("wgpt_matmul", dev.handle, 2, 128, 256, a_d.ptr, w_d.ptr, None, y_d.ptr)   # sizes the workspace
+        _lib.call("wgpt_graph_begin", dev.handle)
+        _lib.call("wgpt_matmul", dev.handle, 2, 128, 256, a_d.ptr, w_d.ptr, None, y_d.ptr)
+        graph = C.c_void_p()
+        _lib.call("wgpt_graph_end", dev.handle, C.byref(graph))
+        _lib.call("wgpt_graph_launch", dev.handle, graph)                                    # fine: nothing moved
+        big_a, big_w = dev.tensor(np.zeros((8, 4096), np.float32)), dev.tensor(np.zeros((4096, 4096), np.float32))
+        big_y = dev.buffer(8 * 4096 * 4)
+        _lib.call("wgpt_matmul", dev.handle, 8, 4096, 4096, big_a.ptr, big_w.ptr, None, big_y.ptr)  # workspace grows
+        with pytest.raises(WgptError) as e:
+            _lib.call("wgpt_graph_launch", dev.handle, graph)
+        assert e.value.code == _lib.ERR_STATE and "recorded again" in e.value.message
+        _lib.call("wgpt_graph_destroy", dev.handle, graph)
+    finally:
+        dev.destroy()
+
+
+def test_matmul_long_shared_dimension_eight_rows(dev, ops, oracle):
+    """8 rows with a shared dimension too long for one CTA's staging buffer: the K split grows until a slice fits."""
+    rng = np.random.default_rng(12)
+    M, K, N = 8, 16384, 256
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = (rng.standard_normal((K, N), dtype=np.float32) * 0.02).astype(np.float32)
+    out = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(np.zeros(N, np.float32))))
+    assert rel_err(out.read(np.float32, M * N).reshape(M, N), oracle.matmul(A, B)) < TOL

@@ -2,7 +2,9 @@
 own all of HBM through their own arena, latency-critical loops, hosts that forbid driver allocations while
 serving). Its split-K scratch is a fixed array inside the library, shared by every call, so the checks here
 are: same answer as wgpt_matmul, also on a second call that finds the first call's leftovers in the array,
-and a clear refusal beyond the array's size. Collected last on purpose."""
+a clear refusal beyond the array's size, and that free device memory does not move across a call (after one
+warm-up call per GPU, which is when the CUDA runtime loads the library's device code). Collected last on
+purpose."""
 import numpy as np
 import pytest
 
@@ -41,5 +43,36 @@ def test_static_scratch_matmul_matches_allocating_entry_point():
         with pytest.raises(WgptError) as e:
             _lib.call("wgpt_matmul_static", dev.handle, 1, big_n, 4, a_d.ptr, w_d.ptr, None, got_d.ptr)
         assert e.value.code == _lib.ERR_SHAPE and "exceeds the built-in scratch" in e.value.message
+    finally:
+        dev.destroy()
+
+
+def test_static_scratch_matmul_allocates_nothing():
+    """After one warm-up call the driver's free-memory figure is the same before and after wgpt_matmul_static,
+    on a shape whose split-K partial sums exceed the workspace a fresh device holds (none); the allocating entry
+    point wgpt_matmul moves that figure on the same shape."""
+    from webgpt_b200 import Device, _lib
+    dev = Device(0)
+    try:
+        rng = np.random.default_rng(78)
+        rows, K, N = 8, 4096, 4096   # split-K partials: a few MiB
+        A = rng.standard_normal((rows, K), dtype=np.float32)
+        W = (rng.standard_normal((K, N), dtype=np.float32) * 0.05).astype(np.float32)
+        a_d, w_d = dev.tensor(A), dev.tensor(W)
+        out_d = dev.buffer(rows * N * 4)
+        _lib.call("wgpt_matmul_static", dev.handle, 1, 64, 64, a_d.ptr, w_d.ptr, None, out_d.ptr)  # warm-up
+        dev.synchronize()
+        free0, _ = dev.mem_info()
+        for _ in range(3):
+            _lib.call("wgpt_matmul_static", dev.handle, rows, N, K, a_d.ptr, w_d.ptr, None, out_d.ptr)
+        dev.synchronize()
+        free1, _ = dev.mem_info()
+        assert free1 == free0
+        got = out_d.read(np.float32, rows * N).reshape(rows, N)
+        assert rel_err(got, A.astype(np.float64) @ W.astype(np.float64)) < TOL
+        _lib.call("wgpt_matmul", dev.handle, rows, N, K, a_d.ptr, w_d.ptr, None, out_d.ptr)  # grows the workspace
+        dev.synchronize()
+        free2, _ = dev.mem_info()
+        assert free2 < free1
     finally:
         dev.destroy()

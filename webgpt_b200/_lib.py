@@ -42,6 +42,7 @@ SIGNATURES = {
     "wgpt_device_synchronize": [vp],
     "wgpt_device_set_precision": [vp, i32],
     "wgpt_device_launch_count": [vp, C.POINTER(u64)],
+    "wgpt_device_mem_info": [vp, C.POINTER(u64), C.POINTER(u64)],
     "wgpt_buffer_create": [vp, u64, vpp],
     "wgpt_buffer_destroy": [vp, vp],
     "wgpt_buffer_write": [vp, vp, u64, vp, u64],

@@ -69,6 +69,7 @@ struct wgpt_device {
   size_t smem_optin;
   void *scratch;  // library-owned workspace (split-K partial sums, temporaries of wgpt_attention)
   size_t scratch_cap;
+  uint64_t scratch_gen;  // bumped whenever the workspace moves: recorded pass lists hold its old address
   int *d_err;     // device-side error word (out-of-range token id)
   float *tc_scratch;  // split-K partial tiles of the tensor-core GEMM (fixed size)
   size_t tc_scratch_bytes;
@@ -141,8 +142,14 @@ static int32_t scratch_reserve(wgpt_device *dev, size_t bytes) {
   size_t cap = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
   CK(cudaMalloc(&dev->scratch, cap));
   dev->scratch_cap = cap;
+  dev->scratch_gen++;
   return WGPT_OK;
 }
+
+// Calls that synchronise the stream (or free memory a recording may name) are not valid while a pass list is
+// being recorded: a synchronise on a capturing stream would invalidate the capture.
+#define NOT_RECORDING(dev, what)                                                                       \
+  REQUIRE(!(dev)->capturing, WGPT_ERR_STATE, "%s is not valid between wgpt_graph_begin and wgpt_graph_end", what)
 
 WGPT_EXPORT int32_t wgpt_abi_version(void) { return WGPT_ABI_VERSION; }
 WGPT_EXPORT const char *wgpt_last_error(void) { return g_err; }
@@ -167,6 +174,7 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->smem_optin = prop.sharedMemPerBlockOptin;
   dev->scratch = nullptr;
   dev->scratch_cap = 0;
+  dev->scratch_gen = 0;
   dev->d_err = nullptr;
   const char *ev = getenv("WGPT_PDL");
   dev->pdl = !(ev && ev[0] == '0');
@@ -205,6 +213,7 @@ WGPT_EXPORT int32_t wgpt_device_destroy(wgpt_device *dev) {
 
 WGPT_EXPORT int32_t wgpt_device_synchronize(wgpt_device *dev) {
   TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_device_synchronize");
   CK(cudaStreamSynchronize(dev->stream));
   return WGPT_OK;
 }
@@ -213,6 +222,16 @@ WGPT_EXPORT int32_t wgpt_device_set_precision(wgpt_device *dev, int32_t mode) {
   TRY(use(dev));
   REQUIRE(mode >= WGPT_PRECISION_FP32 && mode <= WGPT_PRECISION_TF32, WGPT_ERR_ARG, "unknown precision mode %d", mode);
   dev->precision = mode;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_device_mem_info(wgpt_device *dev, uint64_t *free_bytes, uint64_t *total_bytes) {
+  TRY(use(dev));
+  REQUIRE(free_bytes && total_bytes, WGPT_ERR_ARG, "null argument");
+  size_t f = 0, t = 0;
+  CK(cudaMemGetInfo(&f, &t));
+  *free_bytes = f;
+  *total_bytes = t;
   return WGPT_OK;
 }
 
@@ -234,6 +253,7 @@ WGPT_EXPORT int32_t wgpt_buffer_create(wgpt_device *dev, uint64_t bytes, void **
 WGPT_EXPORT int32_t wgpt_buffer_destroy(wgpt_device *dev, void *dptr) {
   TRY(use(dev));
   if (!dptr) return WGPT_OK;
+  NOT_RECORDING(dev, "wgpt_buffer_destroy");
   CK(cudaStreamSynchronize(dev->stream));
   CK(cudaFree(dptr));
   return WGPT_OK;
@@ -242,6 +262,7 @@ WGPT_EXPORT int32_t wgpt_buffer_destroy(wgpt_device *dev, void *dptr) {
 WGPT_EXPORT int32_t wgpt_buffer_write(wgpt_device *dev, void *dst, uint64_t off, const void *src_host, uint64_t bytes) {
   TRY(use(dev));
   REQUIRE(dst && (src_host || !bytes), WGPT_ERR_ARG, "null pointer");
+  NOT_RECORDING(dev, "wgpt_buffer_write");
   if (!bytes) return WGPT_OK;
   CK(cudaMemcpyAsync(static_cast<char *>(dst) + off, src_host, bytes, cudaMemcpyHostToDevice, dev->stream));
   // The source may be pageable and reused by the caller right away.
@@ -252,6 +273,7 @@ WGPT_EXPORT int32_t wgpt_buffer_write(wgpt_device *dev, void *dst, uint64_t off,
 WGPT_EXPORT int32_t wgpt_buffer_read(wgpt_device *dev, const void *src, uint64_t off, void *dst_host, uint64_t bytes) {
   TRY(use(dev));
   REQUIRE(src && (dst_host || !bytes), WGPT_ERR_ARG, "null pointer");
+  NOT_RECORDING(dev, "wgpt_buffer_read");
   if (bytes) CK(cudaMemcpyAsync(dst_host, static_cast<const char *>(src) + off, bytes, cudaMemcpyDeviceToHost, dev->stream));
   CK(cudaStreamSynchronize(dev->stream));
   return WGPT_OK;
@@ -308,6 +330,7 @@ WGPT_EXPORT int32_t wgpt_event_destroy(wgpt_device *dev, void *event) {
 struct wgpt_graph {
   cudaGraphExec_t exec;
   uint64_t launches;
+  uint64_t scratch_gen;  // generation of the device workspace whose address the recording may hold
 };
 
 WGPT_EXPORT int32_t wgpt_graph_begin(wgpt_device *dev) {
@@ -337,6 +360,7 @@ WGPT_EXPORT int32_t wgpt_graph_end(wgpt_device *dev, wgpt_graph **out) {
   wgpt_graph *gr = new wgpt_graph();
   gr->exec = ex;
   gr->launches = n;
+  gr->scratch_gen = dev->scratch_gen;
   *out = gr;
   return WGPT_OK;
 }
@@ -344,6 +368,10 @@ WGPT_EXPORT int32_t wgpt_graph_end(wgpt_device *dev, wgpt_graph **out) {
 WGPT_EXPORT int32_t wgpt_graph_launch(wgpt_device *dev, wgpt_graph *graph) {
   TRY(use(dev));
   REQUIRE(graph != nullptr, WGPT_ERR_ARG, "graph handle is null");
+  NOT_RECORDING(dev, "wgpt_graph_launch");
+  REQUIRE(graph->scratch_gen == dev->scratch_gen, WGPT_ERR_STATE,
+          "the device workspace was re-allocated after this pass list was recorded (a later call needed a larger "
+          "one): the recording names freed memory and must be recorded again");
   CK(cudaGraphLaunch(graph->exec, dev->stream));
   dev->launches += graph->launches;
   return WGPT_OK;
@@ -352,6 +380,7 @@ WGPT_EXPORT int32_t wgpt_graph_launch(wgpt_device *dev, wgpt_graph *graph) {
 WGPT_EXPORT int32_t wgpt_graph_destroy(wgpt_device *dev, wgpt_graph *graph) {
   TRY(use(dev));
   if (!graph) return WGPT_OK;
+  NOT_RECORDING(dev, "wgpt_graph_destroy");
   CK(cudaStreamSynchronize(dev->stream));
   cudaGraphExecDestroy(graph->exec);
   delete graph;
@@ -660,11 +689,17 @@ static int32_t launch_layernorm(wgpt_device *dev, const float *in, size_t ld_in,
 }
 
 // K split for the [K,N]-layout GEMV: enough CTAs for about two per SM, at least 32 k rows per CTA.
-static int kn_ksplit(const wgpt_device *dev, int K, int col_groups) {
+// Each CTA stages its K slice of all M input rows in shared memory, so the split is also at least what makes
+// that slice fit (M * K/ksplit floats beside the 8 KB-per-row reduction buffer).
+static int kn_ksplit(const wgpt_device *dev, int M, int K, int col_groups, size_t red_bytes_per_row = 8 * 32 * 16) {
   int want = (2 * dev->sm_count + col_groups - 1) / col_groups;
   int maxs = K / 32 > 0 ? K / 32 : 1;
   int s = want < maxs ? want : maxs;
-  return s < 1 ? 1 : s;
+  if (s < 1) s = 1;
+  const size_t room = dev->smem_optin - 2048 - (size_t)M * red_bytes_per_row;
+  const size_t klen_fit = room / ((size_t)M * 4) - 8;
+  const int need = (int)(((size_t)K + klen_fit - 1) / klen_fit);
+  return s > need ? s : need;
 }
 
 template <int M>
@@ -702,7 +737,7 @@ static int32_t gemv_kn_with_scratch(wgpt_device *dev, int M, const float *x, con
 // The reference-layout matmul used by the per-operator API: W is [K,N].
 static int32_t matmul_kn(wgpt_device *dev, int M, int K, int N, const float *in, const float *W, const Epilogue &epi) {
   if (M <= 8) {
-    int ksplit = kn_ksplit(dev, K, (N + 127) / 128);
+    int ksplit = kn_ksplit(dev, M, K, (N + 127) / 128);
     TRY(scratch_reserve(dev, (size_t)ksplit * M * N * 4));
     return gemv_kn_with_scratch(dev, M, in, W, K, N, ksplit, static_cast<float *>(dev->scratch), epi);
   }
@@ -798,6 +833,7 @@ WGPT_EXPORT int32_t wgpt_matmul_nk(wgpt_device *dev, int32_t rows, int32_t cols,
 
 WGPT_EXPORT int32_t wgpt_device_check(wgpt_device *dev) {
   TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_device_check");
   return check_err_word(dev, "wgpt_device_check");
 }
 
@@ -879,6 +915,9 @@ WGPT_EXPORT int32_t wgpt_embed(wgpt_device *dev, const uint32_t *idx, int32_t se
   REQUIRE(aligned16(wte) && aligned16(wpe) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
   LAUNCH_PDL(dev, embed_kernel, seq_length, 128, 0, idx, wte, wpe, out, seq_length, seq_length, n_embd, vocab_size,
              (const int *)nullptr, dev->d_err);
+  // While a pass list is being recorded nothing runs yet: an id out of range then surfaces at the next
+  // wgpt_device_check after a replay.
+  if (dev->capturing) return WGPT_OK;
   return check_err_word(dev, "wgpt_embed");
 }
 
@@ -908,7 +947,7 @@ WGPT_EXPORT int32_t wgpt_attention(wgpt_device *dev, int32_t T, int32_t E, float
           WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
   // workspace: q, k, v, o [T,E] + split-K partials
   size_t te = (size_t)T * E;
-  int ksplit = T <= 8 ? kn_ksplit(dev, E, (E + 127) / 128) : 0;
+  int ksplit = T <= 8 ? kn_ksplit(dev, T, E, (E + 127) / 128) : 0;
   size_t part_floats = (size_t)ksplit * T * E;
   TRY(scratch_reserve(dev, (4 * te + part_floats) * 4));
   float *q = static_cast<float *>(dev->scratch), *k = q + te, *v = k + te, *o = v + te, *part = o + te;
@@ -962,7 +1001,7 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
   }
   bool wide = (N % 16 == 0) && M <= 4;
   int col_groups = wide ? (N + 511) / 512 : (N + 127) / 128;
-  int ksplit = kn_ksplit(dev, K, col_groups);
+  int ksplit = kn_ksplit(dev, M, K, col_groups, (size_t)8 * 32 * 4 * (wide ? 4 : 1) * 4);
   TRY(scratch_reserve(dev, (size_t)ksplit * M * N * 4));
   float *part = static_cast<float *>(dev->scratch);
 #define CASE_W(MV) case MV: TRY((launch_int8_gemv_t<MV, 4>(dev, A, Bq, K, N, ksplit, part))); break;
@@ -1054,6 +1093,7 @@ WGPT_EXPORT int32_t wgpt_model_create(wgpt_device *dev, const wgpt_params *param
 WGPT_EXPORT int32_t wgpt_model_destroy(wgpt_model *m) {
   REQUIRE(m != nullptr, WGPT_ERR_ARG, "model handle is null");
   TRY(use(m->dev));
+  NOT_RECORDING(m->dev, "wgpt_model_destroy");
   cudaStreamSynchronize(m->dev->stream);
   for (void *q : m->allocs) cudaFree(q);
   delete m;
@@ -1082,6 +1122,7 @@ static int32_t upload(wgpt_model *m, float *dst, const float *src_host, size_t r
 WGPT_EXPORT int32_t wgpt_model_set_tensor(wgpt_model *m, const char *name, const float *data, uint64_t count) {
   REQUIRE(m && name && data, WGPT_ERR_ARG, "null argument");
   TRY(use(m->dev));
+  NOT_RECORDING(m->dev, "wgpt_model_set_tensor");
   REQUIRE(!m->finalized, WGPT_ERR_STATE, "Model already loaded");
   size_t E = m->p.n_embd, F = 4 * E, V = m->p.vocab_size, C = m->p.n_ctx;
   std::string s(name);
@@ -1221,6 +1262,7 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   *out = nullptr;
   TRY(use(m->dev));
   REQUIRE(m->finalized, WGPT_ERR_STATE, "Model not loaded yet");
+  NOT_RECORDING(m->dev, "wgpt_session_create");
   REQUIRE(n_seq >= 1, WGPT_ERR_SHAPE, "n_seq must be at least 1");
   wgpt_session *s = new wgpt_session();
   s->m = m;
@@ -1261,6 +1303,7 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
 WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
   TRY(use(s->m->dev));
+  NOT_RECORDING(s->m->dev, "wgpt_session_destroy");
   cudaStreamSynchronize(s->m->dev->stream);
   drop_step_graph(s);
   session_free_act(s);
@@ -1419,6 +1462,7 @@ WGPT_EXPORT int32_t wgpt_session_forward(wgpt_session *s, const uint32_t *ids_ho
   REQUIRE(s && ids_host, WGPT_ERR_ARG, "null argument");
   wgpt_device *dev = s->m->dev;
   TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_session_forward");
   REQUIRE(n_tok >= 1, WGPT_ERR_SHAPE, "n_tok must be at least 1");
   REQUIRE(s->len + n_tok <= s->m->p.n_ctx, WGPT_ERR_SHAPE, "sequence length %d + %d exceeds n_ctx %d", s->len, n_tok,
           s->m->p.n_ctx);
@@ -1648,6 +1692,7 @@ WGPT_EXPORT int32_t wgpt_session_set_prompts(wgpt_session *s, const uint32_t *pr
   REQUIRE(s && prompts_host, WGPT_ERR_ARG, "null argument");
   TRY(use(s->m->dev));
   REQUIRE(n_prompt >= 1, WGPT_ERR_SHAPE, "n_prompt must be at least 1");
+  NOT_RECORDING(s->m->dev, "wgpt_session_set_prompts");
   return set_prompts(s, prompts_host, n_prompt);
 }
 
@@ -1664,6 +1709,7 @@ static int32_t generate(wgpt_session *s, int32_t n_new);
 WGPT_EXPORT int32_t wgpt_session_generate(wgpt_session *s, int32_t n_new) {
   REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
   TRY(use(s->m->dev));
+  NOT_RECORDING(s->m->dev, "wgpt_session_generate");
   set_pick_mode(s, 0, 1.0);
   return generate(s, n_new);
 }
@@ -1673,6 +1719,7 @@ WGPT_EXPORT int32_t wgpt_session_generate_sample(wgpt_session *s, int32_t n_new,
   REQUIRE(s && uniforms_host, WGPT_ERR_ARG, "null argument");
   wgpt_device *dev = s->m->dev;
   TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_session_generate_sample");
   REQUIRE(n_new >= 1, WGPT_ERR_SHAPE, "n_new must be at least 1");
   REQUIRE(top_k >= 1 && top_k <= kMaxTopK && top_k <= s->m->p.vocab_size, WGPT_ERR_SHAPE,
           "top_k %d outside 1..%d", top_k, kMaxTopK < s->m->p.vocab_size ? kMaxTopK : s->m->p.vocab_size);
@@ -1755,6 +1802,7 @@ WGPT_EXPORT int32_t wgpt_session_get_new_ids(wgpt_session *s, int32_t n_new, uin
   REQUIRE(s && new_ids_host, WGPT_ERR_ARG, "null argument");
   wgpt_device *dev = s->m->dev;
   TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_session_get_new_ids");
   REQUIRE(n_new >= 1 && n_new <= s->n_generated, WGPT_ERR_STATE, "only %d tokens have been generated", s->n_generated);
   for (int q = 0; q < s->n_seq; q++)
     CK(cudaMemcpyAsync(new_ids_host + (size_t)q * n_new, s->out_ids + (size_t)q * s->out_cap, (size_t)n_new * 4,
@@ -1850,9 +1898,10 @@ WGPT_EXPORT int32_t wgpt_matmul_static(wgpt_device *dev, int32_t rows, int32_t c
   REQUIRE(per_slice <= WGPT_STATIC_SCRATCH_FLOATS, WGPT_ERR_SHAPE,
           "rows*cols = %zu exceeds the built-in scratch of %u floats; use wgpt_matmul", per_slice,
           (unsigned)WGPT_STATIC_SCRATCH_FLOATS);
-  int ksplit = kn_ksplit(dev, shared, (cols + 127) / 128);
-  const size_t fit = WGPT_STATIC_SCRATCH_FLOATS / per_slice;  // >= 1
-  if ((size_t)ksplit > fit) ksplit = (int)fit;
+  const int ksplit = kn_ksplit(dev, rows, shared, (cols + 127) / 128);
+  REQUIRE((size_t)ksplit * per_slice <= WGPT_STATIC_SCRATCH_FLOATS, WGPT_ERR_SHAPE,
+          "the %d K slices of a %dx%dx%d product need %zu floats, the built-in scratch holds %u; use wgpt_matmul",
+          ksplit, rows, cols, shared, (size_t)ksplit * per_slice, (unsigned)WGPT_STATIC_SCRATCH_FLOATS);
   float *part = nullptr;
   TRY(static_scratch_for(dev, &part));
   // Every element of the [ksplit][rows][cols] partial block is written by the first kernel before the second

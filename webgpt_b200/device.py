@@ -75,6 +75,12 @@ class Device:
         _lib.call("wgpt_device_launch_count", self.handle, C.byref(n))
         return n.value
 
+    def mem_info(self):
+        """(free, total) device memory in bytes as the driver reports them."""
+        f, t = C.c_uint64(), C.c_uint64()
+        _lib.call("wgpt_device_mem_info", self.handle, C.byref(f), C.byref(t))
+        return f.value, t.value
+
     def event(self):
         e = C.c_void_p()
         _lib.call("wgpt_event_create", self.handle, C.byref(e))
