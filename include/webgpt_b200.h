@@ -191,6 +191,15 @@ int32_t wgpt_attention(wgpt_device *dev, int32_t seq_length, int32_t n_embd, flo
 int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int32_t N, const float *A, const uint32_t *Bq,
                          const float *scale, float *out);
 
+/* quantizeMatrix (other/int8-gemm.js:25-46) on the device: W is the row-major f32 [K, N] weight; Bq_out receives
+ * [K, N/4] words, byte j of word w in row k = round(W[k, 4w+j] / absmax * 127) & 0xff with the JavaScript
+ * arithmetic (double precision, Math.round halves toward +infinity, :36-42); scale_out[n] = absmax / 127.
+ * per_column != 0 takes absmax per output column (the vector-wise scales the prototype's header asks for, :4),
+ * per_column == 0 over the whole matrix as the prototype does (:29-33). A zero column packs zeros with scale 0.
+ * Feeds wgpt_int8_matmul directly. N % 4 == 0. All pointers are device memory. */
+int32_t wgpt_int8_quantize(wgpt_device *dev, int32_t K, int32_t N, int32_t per_column, const float *W,
+                           uint32_t *Bq_out, float *scale_out);
+
 /* ---- model level: class GPT of model.js ---- */
 
 /* params_gpt.json fields (model.js:289-322). bias is informational (model.js:322). */

@@ -253,6 +253,13 @@ ORC_API void orc_attention(const float *x, int T, int E, int H, float scale, con
 /* int8 prototype, other/int8-gemm.js.
  * JS Math.round rounds halves toward +infinity: floor(x + 0.5). */
 static double js_round(double x) { return floor(x + 0.5); }
+/* Math.round((x / absmax) * 127): three separately rounded double operations, as JavaScript evaluates them;
+ * the volatile keeps a compiler from contracting the multiply and the + 0.5 into one fused operation. */
+static double js_quant(double x, double absmax) {
+  volatile double t = x / absmax;
+  t = t * 127.0;
+  return js_round(t);
+}
 
 /* quantizeMatrix, other/int8-gemm.js:25-46: word w packs elements 4w..4w+3 of the flattened
  * row-major matrix, byte j = round(x/absmax*127) & 0xff. count must be a multiple of 4.
@@ -261,11 +268,42 @@ ORC_API void orc_int8_quantize(const float *x, size_t count, double absmax, int3
   for (size_t i = 0; i < count; i += 4) {
     uint32_t w = 0;
     for (int j = 0; j < 4; j++) {
-      int32_t q = (int32_t)js_round(((double)x[i + j] / absmax) * 127.0);
+      int32_t q = (int32_t)js_quant((double)x[i + j], absmax);
       w |= ((uint32_t)q & 0xffu) << (8 * j);
     }
     packed[i / 4] = (int32_t)w;
   }
+}
+
+/* quantizeMatrix with the vector-wise scales its header asks for (other/int8-gemm.js:4): the same expression
+ * round(x / absmax * 127) & 0xff (:36-42), packed four per word along N, but with absmax taken per output column n
+ * of the row-major [K, N] matrix (:29-33 take it over the whole matrix). scale[n] = absmax_n / 127 as f32 is the
+ * factor the dequant-GEMM multiplies by. A column of zeros quantises to zeros with scale 0 (the JS expression gives
+ * NaN & 0xff = 0 there). per_column == 0 reproduces the prototype: one absmax for the matrix. N % 4 == 0. */
+ORC_API void orc_int8_quantize_matrix(const float *w, int K, int N, int per_column, int32_t *packed, float *scale) {
+  double *amax = calloc((size_t)N, sizeof(double));
+  for (int k = 0; k < K; k++)
+    for (int n = 0; n < N; n++) {
+      double a = fabs((double)w[(size_t)k * N + n]);
+      if (a > amax[n]) amax[n] = a;
+    }
+  if (!per_column) {
+    double g = 0.0;
+    for (int n = 0; n < N; n++) if (amax[n] > g) g = amax[n];
+    for (int n = 0; n < N; n++) amax[n] = g;
+  }
+  for (int n = 0; n < N; n++) scale[n] = (float)(amax[n] / 127.0);
+  for (int k = 0; k < K; k++)
+    for (int n = 0; n < N; n += 4) {
+      uint32_t word = 0;
+      for (int j = 0; j < 4; j++) {
+        double a = amax[n + j];
+        int32_t q = a > 0.0 ? (int32_t)js_quant((double)w[(size_t)k * N + n + j], a) : 0;
+        word |= ((uint32_t)q & 0xffu) << (8 * j);
+      }
+      packed[((size_t)k * N + n) / 4] = (int32_t)word;
+    }
+  free(amax);
 }
 
 /* The integer half of unpackInt8x4, other/int8-gemm.js:126-132: lane j = (v << (24-8j)) >> 24

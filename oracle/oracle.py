@@ -69,6 +69,7 @@ def lib():
         L.orc_generate_sample.argtypes = [C.c_void_p, u32p, C.c_int, C.c_int, C.c_int, C.c_double, f64p, u32p]
         L.orc_int8_quantize.argtypes = [f32p, C.c_size_t, C.c_double, i32p]
         L.orc_int8_unpack.argtypes = [i32p, C.c_size_t, C.POINTER(C.c_int8)]
+        L.orc_int8_quantize_matrix.argtypes = [f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]
     return _LIB
 
 
@@ -187,6 +188,16 @@ def int8_quantize(x, absmax):
     out = np.empty(x.size // 4, np.int32)
     lib().orc_int8_quantize(px, x.size, float(absmax), out.ctypes.data_as(i32p))
     return out
+
+
+def int8_quantize_matrix(w, per_column=True):
+    """Returns (packed [K, N/4] int32, scale [N] f32) for a row-major [K, N] matrix."""
+    w, pw = _f(w)
+    K, N = w.shape
+    packed = np.empty((K, N // 4), np.int32)
+    scale = np.empty(N, np.float32)
+    lib().orc_int8_quantize_matrix(pw, K, N, int(per_column), packed.ctypes.data_as(i32p), scale.ctypes.data_as(f32p))
+    return packed, scale
 
 
 def int8_unpack(packed):

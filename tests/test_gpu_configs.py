@@ -176,8 +176,8 @@ def test_gpt2_xl_full_depth(oracle):
         assert rel_err(lg, ref_775) < TF32X3
         # the next tokens of a greedy run from there stay the same whether decoded one at a time or re-run
         nxt = int(np.argmax(lg))
-        again = gpt.run(np.concatenate([ids[:776], [nxt]]).astype(np.uint32))
         step = s.forward(np.array([nxt], np.uint32))[0]
+        again = gpt.run(np.concatenate([ids[:776], [nxt]]).astype(np.uint32))  # resets the shared session
         assert rel_err(step, again) < TF32X3
     finally:
         gpt.destroy()

@@ -322,6 +322,32 @@ def test_load_from_weight_folder(tmp_path, fused):
         b.destroy()
 
 
+def test_load_linear_layout_and_bias_free_folder(tmp_path):
+    """The second on-disk convention (nn.Linear [out, in] matrices and block_size, condensed/condensed.js:1726,
+    1765-1784) and a bias-free checkpoint (bias files absent, model.js:322) load to the same logits as the same
+    weights handed over in memory."""
+    from webgpt_b200 import GPT, export
+    params = synth.CONFIGS["tiny"]
+    w = synth.make_weights(params, seed=8, std=0.2, ln_random=True)
+    for k in w:
+        if k.endswith(".bias"):
+            w[k] = np.zeros_like(w[k])
+    cfg = {"n_layer": 2, "n_head": 2, "n_embd": 32, "block_size": 24, "vocab_size": 50, "bias": False}
+    sd = {k: v for k, v in w.items() if not k.endswith(".bias")}
+    folder = str(tmp_path / "lin")
+    export.export_model(sd, cfg, folder, weight_layout="out_in")
+    a = GPT(folder)
+    a.initialize()
+    b = make_gpt(params, w)
+    try:
+        ids = synth.make_tokens(params["vocab_size"], 9, seed=2)
+        assert np.array_equal(a.run(ids), b.run(ids))
+        assert list(a.generate(ids, 5, 1)) == list(b.generate(ids, 5, 1))
+    finally:
+        a.destroy()
+        b.destroy()
+
+
 def test_whole_token_decode_kernel_opt_in(oracle, monkeypatch):
     """WGPT_PERSISTENT=1 routes single-sequence decode through decode_persistent_kernel (grid barriers instead
     of kernel boundaries); same tokens and logits as the oracle."""

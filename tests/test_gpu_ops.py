@@ -292,3 +292,29 @@ def test_matmul_long_shared_dimension_eight_rows(dev, ops, oracle):
     B = (rng.standard_normal((K, N), dtype=np.float32) * 0.02).astype(np.float32)
     out = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(np.zeros(N, np.float32))))
     assert rel_err(out.read(np.float32, M * N).reshape(M, N), oracle.matmul(A, B)) < TOL
+
+
+@pytest.mark.parametrize("per_column", [True, False])
+@pytest.mark.parametrize("K,N", [(24, 16), (768, 3072), (1600, 6400), (100, 8)])
+def test_int8_quantize_bit_exact(dev, oracle, K, N, per_column):
+    """wgpt_int8_quantize against the oracle's quantiser: identical words and scales (JS double arithmetic,
+    Math.round halves toward +infinity, & 0xff, 4 per word along N, other/int8-gemm.js:25-62), including a zero
+    column and values that sit exactly on a rounding half; the result feeds wgpt_int8_matmul."""
+    from webgpt_b200 import _lib
+    rng = np.random.default_rng(K + N)
+    w = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    w[:, 3] = 0.0
+    w[1, 2] = np.float32(2.5) * np.abs(w[:, 2]).max() / np.float32(127)
+    w[2, 2] = -w[1, 2]
+    ref_q, ref_s = oracle.int8_quantize_matrix(w, per_column=per_column)
+    w_d, q_d, s_d = dev.tensor(w), dev.buffer(K * N), dev.buffer(N * 4)
+    _lib.call("wgpt_int8_quantize", dev.handle, K, N, int(per_column), w_d.ptr, q_d.ptr, s_d.ptr)
+    assert np.array_equal(q_d.read(np.int32, K * N // 4).reshape(K, N // 4), ref_q)
+    assert np.array_equal(s_d.read(np.float32, N), ref_s)
+    if N % 8 == 0 and K % 4 == 0:
+        A = rng.standard_normal((2, K), dtype=np.float32)
+        a_d, o_d = dev.tensor(A), dev.buffer(2 * N * 4)
+        _lib.call("wgpt_int8_matmul", dev.handle, 2, K, N, a_d.ptr, q_d.ptr, s_d.ptr, o_d.ptr)
+        got = o_d.read(np.float32, 2 * N).reshape(2, N)
+        assert rel_err(got, oracle.int8_matmul(A, ref_q, ref_s, N)) < TOL
+        assert np.max(np.abs(got - A @ w)) < 0.1     # the prototype's acceptance rule, other/int8-gemm.js:321

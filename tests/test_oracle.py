@@ -235,3 +235,30 @@ def test_sample_topk_golden(oracle):
     g = load_golden("sampling_kat.npz")
     for r, k, t, u, pick in zip(g["row"], g["top_k"], g["temperature"], g["u"], g["pick"]):
         assert oracle.sample_topk(g["logits"][r], int(k), float(t), float(u)) == int(pick)
+
+
+def test_int8_quantize_matrix_matches_the_flat_quantiser(oracle):
+    """The matrix form with one absmax for the matrix is the prototype's quantizeMatrix (other/int8-gemm.js:25-46)
+    word for word; with per-column maxima each column equals the flat quantiser run on that column with its own
+    absmax, and dequantised values stay within half a step of the weights."""
+    rng = np.random.default_rng(3)
+    K, N = 24, 16
+    w = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    w[:, 5] = 0.0                                  # a zero column
+    w[3, 2] = np.float32(0.5) * np.abs(w[:, 2]).max() / np.float32(127)   # a rounding half
+    packed, scale = oracle.int8_quantize_matrix(w, per_column=False)
+    absmax = float(np.abs(w).max())
+    assert np.array_equal(packed.reshape(-1), oracle.int8_quantize(w.reshape(-1), absmax))
+    assert np.all(scale == np.float32(absmax / 127.0))
+    packed, scale = oracle.int8_quantize_matrix(w, per_column=True)
+    q = oracle.int8_unpack(packed.reshape(-1)).reshape(K, N)
+    for n in range(N):
+        a = float(np.abs(w[:, n]).max())
+        if a == 0.0:
+            assert not q[:, n].any() and scale[n] == 0.0
+            continue
+        col = np.repeat(w[:, n], 4)                # the flat quantiser packs 4 consecutive values
+        ref = oracle.int8_unpack(oracle.int8_quantize(col, a))[::4]
+        assert np.array_equal(q[:, n], ref)
+        assert scale[n] == np.float32(a / 127.0)
+    assert np.max(np.abs(q * scale[None, :] - w)) <= 0.5001 * scale.max()

@@ -15,6 +15,7 @@
 
 #include "attention.cuh"
 #include "common.cuh"
+#include "decode_fused.cuh"
 #include "decode_persistent.cuh"
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
@@ -79,6 +80,7 @@ struct wgpt_device {
   bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
   uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
+  bool fused_decode;  // single-sequence decode with two kernels per block (WGPT_FUSED_DECODE=0 turns it off)
 };
 
 #define LAUNCH(dev, kernel, grid, block, smem, ...)                       \
@@ -90,6 +92,37 @@ struct wgpt_device {
 
 // Launch for kernels that call pdl_wait() before touching anything an earlier kernel wrote: with dev->pdl they
 // carry the programmatic-serialisation attribute and may start while their predecessor is still running.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_ex(bool pdl, int cluster_z, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid,
+                             dim3 block, size_t smem, Args... args);
+
+// Launch with thread-block clusters of cluster_x CTAs along x (and programmatic dependent launch if pdl).
+template <typename P>
+static cudaError_t launch_cluster_x(bool pdl, int cluster_x, cudaStream_t stream, void (*kernel)(P), dim3 grid,
+                                    dim3 block, size_t smem, const P &arg) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  attr[n].id = cudaLaunchAttributeClusterDimension;
+  attr[n].val.clusterDim.x = (unsigned)cluster_x;
+  attr[n].val.clusterDim.y = 1;
+  attr[n].val.clusterDim.z = 1;
+  n++;
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, arg);
+}
+
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_ex(bool pdl, int cluster_z, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid,
                              dim3 block, size_t smem, Args... args) {
@@ -184,6 +217,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->block_gemv = !(ev && ev[0] == '0');
   ev = getenv("WGPT_PERSISTENT");
   dev->persistent = ev && ev[0] == '1';  // measured slower than the kernel chain on B200, so opt-in
+  ev = getenv("WGPT_FUSED_DECODE");
+  dev->fused_decode = !(ev && ev[0] == '0');
   dev->capturing = false;
   dev->capture_launch0 = 0;
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
@@ -963,6 +998,23 @@ WGPT_EXPORT int32_t wgpt_attention(wgpt_device *dev, int32_t T, int32_t E, float
   return mm(o, linW, linB, out);
 }
 
+WGPT_EXPORT int32_t wgpt_int8_quantize(wgpt_device *dev, int32_t K, int32_t N, int32_t per_column, const float *W,
+                                       uint32_t *Bq_out, float *scale_out) {
+  TRY(use(dev));
+  REQUIRE(W && Bq_out && scale_out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(K >= 1 && N >= 4 && N % 4 == 0, WGPT_ERR_SHAPE, "quantise needs K >= 1 and N a positive multiple of 4");
+  REQUIRE(aligned16(W) && aligned16(Bq_out) && aligned16(scale_out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  int slices = K / 64 > 0 ? K / 64 : 1;
+  if (slices > 64) slices = 64;
+  TRY(scratch_reserve(dev, ((size_t)slices + 1) * N * 4));
+  float *part = static_cast<float *>(dev->scratch), *absmax = part + (size_t)slices * N;
+  LAUNCH(dev, int8_absmax_kernel, dim3((N + 127) / 128, slices), 128, 0, W, K, N, part);
+  LAUNCH(dev, int8_scale_kernel, 1, 256, 0, (const float *)part, slices, N, per_column ? 1 : 0, absmax, scale_out);
+  LAUNCH(dev, int8_pack_kernel, grid_for((size_t)K * (N / 4), 256, dev->sm_count), 256, 0, W, (const float *)absmax,
+         K, N, Bq_out);
+  return WGPT_OK;
+}
+
 template <int M, int VEC>
 static int32_t launch_int8_gemv_t(wgpt_device *dev, const float *x, const uint32_t *Bq, int K, int N, int ksplit,
                                   float *part) {
@@ -1026,6 +1078,20 @@ struct LayerWeights {
   float *ln1_g, *ln1_b, *wqkv_t, *bqkv, *wo_t, *bo, *ln2_g, *ln2_b, *wfc_t, *bfc, *wpr_t, *bpr;
   // low parts of the four matrices for 3xTF32 (w - tf32(w), same [N,K] layout), filled by wgpt_model_finalize
   float *wqkv_lo = nullptr, *wo_lo = nullptr, *wfc_lo = nullptr, *wpr_lo = nullptr;
+  // single-sequence fused decode (decode_fused.cuh): per-(head, cluster rank) blocks of the attention weights and
+  // the MLP down-projection in the [K,N] orientation, filled by wgpt_model_finalize when the plan applies
+  float *attn_blk = nullptr, *wpr_kn = nullptr;
+};
+
+// Launch plan of the two-kernels-per-block decode for one model on one device; ok == false keeps the kernel chain.
+struct FusedPlan {
+  bool ok = false;
+  int cs = 0;              // cluster size of attn_block_kernel
+  size_t blk_floats = 0;
+  int proj_parts = 0, red_a = 0;
+  size_t smem_a = 0;
+  int units = 0, n_mlp = 0 /* CTAs */, n_mlp_rows = 0 /* clusters = partial rows */, wk = 0, down_parts = 0, red_b = 0;
+  size_t smem_b = 0;
 };
 
 struct wgpt_model {
@@ -1039,6 +1105,7 @@ struct wgpt_model {
   bool finalized;
   std::vector<void *> allocs;
   LayerPtrs *d_layers;  // device copy of the per-layer weight pointers (decode_persistent_kernel)
+  FusedPlan fused;
 };
 
 static int32_t model_alloc(wgpt_model *m, float **p, size_t floats) {
@@ -1165,6 +1232,145 @@ WGPT_EXPORT int32_t wgpt_model_set_tensor(wgpt_model *m, const char *name, const
   return WGPT_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------ fused decode plan
+template <int HS, int CS>
+static int32_t attn_block_launch_t(wgpt_device *dev, const FusedPlan &fp, int H, const AttnBlockParams &a,
+                                   int *max_clusters) {
+  auto kern = attn_block_kernel<HS, CS>;
+  CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp.smem_a));
+  // the whole shared-memory carveout: the next kernel's CTA must fit on the SM beside this one to fetch its
+  // weights while this one runs
+  CK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+  if (max_clusters != nullptr) {  // planning: how many clusters of this shape can be resident at once
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(H * CS);
+    cfg.blockDim = dim3(kAttnBlockThreads);
+    cfg.dynamicSmemBytes = fp.smem_a;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CK(cudaOccupancyMaxActiveClusters(max_clusters, kern, &cfg));
+    return WGPT_OK;
+  }
+  CK(launch_cluster_x(dev->pdl, CS, dev->stream, kern, dim3(H * CS), dim3(kAttnBlockThreads), fp.smem_a, a));
+  dev->launches++;
+  return WGPT_OK;
+}
+
+// Dispatch on (head size, cluster size). With max_clusters != nullptr nothing is launched (occupancy query).
+static int32_t attn_block_launch(wgpt_device *dev, const FusedPlan &fp, int hs, int H, const AttnBlockParams &a,
+                                 int *max_clusters = nullptr) {
+#define CASE_A(HSV, CSV) \
+  if (hs == HSV && fp.cs == CSV) return attn_block_launch_t<HSV, CSV>(dev, fp, H, a, max_clusters);
+  CASE_A(128, 8) CASE_A(64, 8) CASE_A(32, 8) CASE_A(16, 8) CASE_A(8, 8)
+  CASE_A(128, 4) CASE_A(64, 4) CASE_A(32, 4) CASE_A(16, 4) CASE_A(8, 4) CASE_A(4, 4)
+#undef CASE_A
+  return fail(WGPT_ERR_UNSUPPORTED, "no fused attention kernel for head_size %d with clusters of %d", hs, fp.cs);
+}
+
+template <int HS, int CS>
+static size_t attn_block_smem_t(int E, int red) { return attn_block_smem_floats<HS, CS>(E, red) * 4; }
+
+static size_t attn_block_smem(int hs, int cs, int E, int red) {
+  // 3*(hs/cs)*E + E + red + 3hs + cs*(hs+4) + hs + 8 floats (attn_block_smem_floats)
+  return ((size_t)3 * (hs / cs) * E + (size_t)E + red + 3 * hs + (size_t)cs * (hs + 4) + hs + 8) * 4;
+}
+
+// Decides whether single-sequence decode of this model can run as two kernels per block on this device: both
+// kernels' weight slices must fit in one SM's shared memory side by side (each prefetches its weights while the
+// other is still running), and one cluster per head must be resident at once.
+static int32_t fused_plan(wgpt_model *m) {
+  wgpt_device *dev = m->dev;
+  FusedPlan &fp = m->fused;
+  fp = FusedPlan();
+  const int E = m->p.n_embd, H = m->p.n_head, hs = m->hs, F = 4 * E;
+  if (!dev->fused_decode || E % 32 != 0) return WGPT_OK;
+  // MLP kernel: clusters of kMlpCluster CTAs, as many as can be resident at once (at most one CTA per SM), each
+  // CTA a contiguous slice of the hidden units
+  if ((E / 4) % kMlpCluster != 0 || E / 4 > kAttnBlockThreads) return WGPT_OK;
+  auto mlp = mlp_block_kernel;
+  int clusters = dev->sm_count / kMlpCluster;
+  for (int attempt = 0; attempt < 2; attempt++) {
+    fp.n_mlp = clusters * kMlpCluster;
+    if (fp.n_mlp > F) fp.n_mlp = (F / kMlpCluster) * kMlpCluster;
+    if (fp.n_mlp < kMlpCluster) return WGPT_OK;
+    fp.n_mlp_rows = fp.n_mlp / kMlpCluster;
+    fp.units = (F + fp.n_mlp - 1) / fp.n_mlp;
+    fp.wk = 1;
+    while (fp.units * fp.wk < 2 * (kMlpBlockThreads / 32) && fp.wk < 8 && (E / 4) / (fp.wk * 2) >= 32) fp.wk *= 2;
+    fp.down_parts = kMlpBlockThreads / (E / 4);
+    if (fp.down_parts > fp.units) fp.down_parts = fp.units;
+    if (fp.down_parts < 1) return WGPT_OK;
+    int red = fp.units * fp.wk;
+    if (red < 2 * (kMlpBlockThreads / 32)) red = 2 * (kMlpBlockThreads / 32);
+    fp.red_b = (red + 3) & ~3;
+    fp.smem_b = mlp_block_smem_floats(E, fp.units, fp.red_b) * 4;
+    if (fp.smem_b > (size_t)dev->smem_optin) return WGPT_OK;
+    // limits of the batched row sums (warp_rows_partial / halfwarp_rows_sum in decode_fused.cuh)
+    if (fp.n_mlp_rows > (kAttnBlockThreads / 32) * kAttnSumRows || H > 2 * kMlpSumRows ||
+        (E / 4) / kMlpCluster > 16 * (kMlpBlockThreads / 32))
+      return WGPT_OK;
+    CK(cudaFuncSetAttribute(mlp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp.smem_b));
+    CK(cudaFuncSetAttribute(mlp, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(fp.n_mlp);
+    cfg.blockDim = dim3(kMlpBlockThreads);
+    cfg.dynamicSmemBytes = fp.smem_b;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kMlpCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int max_clusters = 0;
+    CK(cudaOccupancyMaxActiveClusters(&max_clusters, mlp, &cfg));
+    if (getenv("WGPT_DEBUG_PLAN"))
+      fprintf(stderr, "[wgpt plan] mlp: grid %d units %d smem %zu -> max active clusters of %d: %d\n", fp.n_mlp, fp.units,
+              fp.smem_b, kMlpCluster, max_clusters);
+    if (max_clusters >= fp.n_mlp_rows) break;
+    if (attempt == 1 || max_clusters < 1) return WGPT_OK;
+    clusters = max_clusters;  // fewer clusters fit side by side than SMs / 4: size the grid to what is resident
+  }
+  for (int cs : {8, 4}) {
+    if (hs % cs != 0 || E % (4 * cs) != 0 || (cs == 8 && hs < 8)) continue;
+    const int ncolA = E / cs, ncol4 = ncolA / 4;
+    if (ncolA > kAttnBlockThreads || ncol4 > 32) continue;
+    fp.cs = cs;
+    (void)ncol4;
+    fp.proj_parts = kAttnBlockThreads / ncolA < hs ? kAttnBlockThreads / ncolA : hs;
+    int red = (kAttnBlockThreads / 32) * (hs + 4);
+    if (red < (kAttnBlockThreads / 32) * 32 * 4) red = (kAttnBlockThreads / 32) * 32 * 4;  // [warps][32] float4 row sums
+    if (fp.proj_parts * ncolA > red) red = fp.proj_parts * ncolA;
+    fp.red_a = (red + 3) & ~3;
+    fp.blk_floats = (size_t)3 * (hs / cs) * E + (size_t)hs * ncolA;
+    fp.smem_a = attn_block_smem(hs, cs, E, fp.red_a);
+    // side by side on one SM, 1 KB reserved per resident CTA
+    if (getenv("WGPT_DEBUG_PLAN"))
+      fprintf(stderr, "[wgpt plan] attn cluster %d: smem %zu + mlp %zu (limit %zu)\n", cs, fp.smem_a, fp.smem_b,
+              (size_t)dev->smem_optin + 1024 - 2048);
+    if (fp.smem_a + fp.smem_b + 2048 > (size_t)dev->smem_optin + 1024) continue;
+    int max_clusters = 0;
+    AttnBlockParams dummy;
+    memset(&dummy, 0, sizeof dummy);
+    if (attn_block_launch(dev, fp, hs, H, dummy, &max_clusters) != WGPT_OK) continue;
+    if (getenv("WGPT_DEBUG_PLAN"))
+      fprintf(stderr, "[wgpt plan] attn: cluster %d smem %zu -> max active clusters %d (need %d)\n", cs, fp.smem_a,
+              max_clusters, H);
+    if (max_clusters < H) continue;
+    fp.ok = true;
+    break;
+  }
+  return WGPT_OK;
+}
+
 WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
   REQUIRE(m != nullptr, WGPT_ERR_ARG, "model handle is null");
   for (size_t i = 0; i < m->have.size(); i++)
@@ -1188,6 +1394,20 @@ WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
       }
     }
   }
+  TRY(fused_plan(m));
+  if (m->fused.ok) {
+    const int E = m->p.n_embd, F = 4 * E, H = m->p.n_head;
+    const size_t blk_total = m->fused.blk_floats * H * m->fused.cs;
+    for (auto &L : m->layers) {
+      if (L.attn_blk == nullptr) TRY(model_alloc(m, &L.attn_blk, blk_total));
+      if (L.wpr_kn == nullptr) TRY(model_alloc(m, &L.wpr_kn, (size_t)F * E));
+      LAUNCH(m->dev, fused_attn_relayout_kernel, grid_for(blk_total, 256, m->dev->sm_count), 256, 0,
+             (const float *)L.wqkv_t, (const float *)L.wo_t, L.attn_blk, E, H, m->hs, m->fused.cs);
+      // wpr_t is [E, F] (N rows of K); its transpose is the reference's [K, N] orientation
+      dim3 tg((unsigned)((F + 31) / 32), (unsigned)((E + 31) / 32));
+      LAUNCH(m->dev, transpose_kernel, tg, dim3(32, 8), 0, (const float *)L.wpr_t, L.wpr_kn, E, F);
+    }
+  }
   CK(cudaMalloc(reinterpret_cast<void **>(&m->d_layers), lp.size() * sizeof(LayerPtrs)));
   m->allocs.push_back(m->d_layers);
   CK(cudaMemcpyAsync(m->d_layers, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice, m->dev->stream));
@@ -1207,6 +1427,8 @@ struct wgpt_session {
   int n_split;
   float *x, *h, *q, *o, *f, *logits;
   float *kc, *vc;  // [n_layer][n_seq][n_ctx][E]
+  float *fx_a = nullptr, *fx_b = nullptr;     // fused decode: residual stream entering the attention / MLP kernel
+  float *fpart_a = nullptr, *fpart_b = nullptr;  // fused decode: partial results [n_head][E] and [mlp CTAs][E]
   float *attn_part;  // decode-attention partials, [n_seq][n_head][n_split][hs + 4]
   unsigned int *attn_cnt;
   uint32_t *ids, *next_ids, *out_ids;
@@ -1286,11 +1508,19 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_val, (size_t)n_seq * p.vocab_size * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_idx, (size_t)n_seq * p.vocab_size * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->d_pos, 2 * sizeof(int));
+  if (e == cudaSuccess && m->fused.ok && n_seq == 1) {
+    const size_t E = p.n_embd;
+    e = cudaMalloc(&s->fx_a, E * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&s->fx_b, E * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&s->fpart_a, (size_t)p.n_head * E * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&s->fpart_b, (size_t)m->fused.n_mlp * E * 4);
+  }
   if (e == cudaSuccess) e = cudaMemsetAsync(s->attn_cnt, 0, ((size_t)n_seq * p.n_head + 1) * 4, m->dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), m->dev->stream);
   if (e != cudaSuccess) {
     cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
     cudaFree(s->next_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
+    cudaFree(s->fx_a); cudaFree(s->fx_b); cudaFree(s->fpart_a); cudaFree(s->fpart_b);
     delete s;
     return fail(e == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "session allocation: %s",
                 cudaGetErrorString(e));
@@ -1311,6 +1541,7 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
   cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
   cudaFree(s->d_uniform);
+  cudaFree(s->fx_a); cudaFree(s->fx_b); cudaFree(s->fpart_a); cudaFree(s->fpart_b);
   delete s;
   return WGPT_OK;
 }
@@ -1338,6 +1569,55 @@ WGPT_EXPORT int32_t wgpt_session_length(wgpt_session *s, int32_t *length) {
 // Leaves the logits of each sequence's newest position in s->logits. Does not advance the position.
 static int32_t pick_and_advance(wgpt_session *s, int n_tok);
 
+
+// The transformer blocks of a single-sequence decode step as two kernels per block (decode_fused.cuh); leaves the
+// residual stream before ln_f in s->x.
+static int32_t forward_blocks_fused(wgpt_session *s, const uint32_t *ids) {
+  wgpt_model *m = s->m;
+  wgpt_device *dev = m->dev;
+  const wgpt_params &p = m->p;
+  const FusedPlan &fp = m->fused;
+  const int E = p.n_embd, F = 4 * E, H = p.n_head;
+  const size_t kv_layer = (size_t)p.n_ctx * E;
+  auto mlp = mlp_block_kernel;
+  if (fp.smem_b > 48 * 1024) CK(cudaFuncSetAttribute(mlp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp.smem_b));
+  CK(cudaFuncSetAttribute(mlp, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+  for (int l = 0; l < p.n_layer; l++) {
+    const LayerWeights &L = m->layers[l];
+    AttnBlockParams a;
+    memset(&a, 0, sizeof a);
+    if (l == 0) {
+      a.ids = ids; a.wte = m->wte; a.wpe = m->wpe; a.vocab = p.vocab_size;
+    } else {
+      a.xin = s->fx_b; a.part_in = s->fpart_b; a.bias_in = m->layers[l - 1].bpr; a.n_part = fp.n_mlp_rows;
+    }
+    a.x_out = s->fx_a;
+    a.gamma = L.ln1_g; a.beta = L.ln1_b;
+    a.wblk = L.attn_blk; a.blk_floats = fp.blk_floats; a.bqkv = L.bqkv;
+    a.kc = s->kc + (size_t)l * kv_layer; a.vc = s->vc + (size_t)l * kv_layer;
+    a.part_out = s->fpart_a;
+    a.pos = s->d_pos;
+    a.E = E; a.H = H; a.scale = m->scale;
+    a.proj_parts = fp.proj_parts; a.red_floats = fp.red_a;
+    a.err = dev->d_err;
+    TRY(attn_block_launch(dev, fp, m->hs, H, a));
+    MlpBlockParams b;
+    memset(&b, 0, sizeof b);
+    b.xin = s->fx_a; b.part_in = s->fpart_a; b.bias_in = L.bo; b.n_part = H;
+    b.x_out = s->fx_b;
+    b.gamma = L.ln2_g; b.beta = L.ln2_b;
+    b.wfc_t = L.wfc_t; b.bfc = L.bfc; b.wpr_kn = L.wpr_kn;
+    b.part_out = s->fpart_b;
+    b.E = E; b.F = F; b.units = fp.units; b.wk = fp.wk; b.down_parts = fp.down_parts; b.red_floats = fp.red_b;
+    b.err = dev->d_err;
+    CK(launch_cluster_x(dev->pdl, kMlpCluster, dev->stream, mlp, dim3(fp.n_mlp), dim3(kMlpBlockThreads), fp.smem_b, b));
+    dev->launches++;
+  }
+  LAUNCH_PDL(dev, finish_row_kernel, (E / 4 + 31) / 32, 256, 0, (const float *)s->fx_b,
+             (const float *)m->layers[p.n_layer - 1].bpr, (const float *)s->fpart_b, fp.n_mlp_rows, E, s->x);
+  return WGPT_OK;
+}
+
 // With pick, the greedy choice of every sequence is also made (next_ids, out_ids) and the position advanced.
 static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pick = false) {
   wgpt_model *m = s->m;
@@ -1346,8 +1626,10 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   const int E = p.n_embd, F = 4 * E, H = p.n_head, hs = m->hs, M = s->n_seq * n_tok;
   const size_t kv_layer = (size_t)s->n_seq * p.n_ctx * E;
 
-  LAUNCH_PDL(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size,
-             (const int *)s->d_pos, dev->d_err);
+  const bool fused = n_tok == 1 && s->n_seq == 1 && m->fused.ok && s->fx_a != nullptr;
+  if (!fused)
+    LAUNCH_PDL(dev, embed_kernel, M, 128, 0, ids, m->wte, m->wpe, s->x, M, n_tok, E, p.vocab_size,
+               (const int *)s->d_pos, dev->d_err);
 
   // s->h already holds the LayerNorm of s->x that the next product wants (left there by the split-K second
   // stage of the product that wrote s->x)
@@ -1373,7 +1655,8 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     return WGPT_OK;
   };
 
-  for (int l = 0; l < p.n_layer; l++) {
+  if (fused) TRY(forward_blocks_fused(s, ids));
+  for (int l = 0; l < (fused ? 0 : p.n_layer); l++) {
     const LayerWeights &L = m->layers[l];
     float *kc = s->kc + (size_t)l * kv_layer, *vc = s->vc + (size_t)l * kv_layer;
     SplitHandoff qkv_slices;

@@ -16,6 +16,65 @@ __device__ __forceinline__ void unpack_int8x4(uint32_t word, float (&f)[4]) {
   f[3] = (float)(v >> 24);
 }
 
+// quantizeMatrix, other/int8-gemm.js:25-46, on the device. Pass 1: |w| maxima per output column of the row-major
+// [K, N] matrix (the prototype's header asks for vector-wise scales, :4), one thread per column per k slice,
+// partial maxima [gridDim.y][N]. The maximum is order-independent, so no fixed order is needed for exactness.
+__global__ void int8_absmax_kernel(const float *__restrict__ w, int K, int N, float *__restrict__ part) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const int kb = (int)(((long long)K * blockIdx.y) / gridDim.y), ke = (int)(((long long)K * (blockIdx.y + 1)) / gridDim.y);
+  float a = 0.f;
+  for (int k = kb; k < ke; k++) a = fmaxf(a, fabsf(w[(size_t)k * N + n]));
+  part[(size_t)blockIdx.y * N + n] = a;
+}
+// Pass 2: column maxima from the partial maxima (per_column == 0: one maximum for the whole matrix, the
+// prototype's own rule :29-33), scale[n] = absmax_n / 127 in double rounded to f32.
+__global__ void int8_scale_kernel(const float *__restrict__ part, int slices, int N, int per_column,
+                                  float *__restrict__ absmax, float *__restrict__ scale) {
+  __shared__ float red[256];
+  const int tid = threadIdx.x;
+  float g = 0.f;
+  for (int n = tid; n < N; n += 256) {
+    float a = 0.f;
+    for (int s = 0; s < slices; s++) a = fmaxf(a, part[(size_t)s * N + n]);
+    absmax[n] = a;
+    g = fmaxf(g, a);
+  }
+  red[tid] = g;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
+    __syncthreads();
+  }
+  g = red[0];
+  for (int n = tid; n < N; n += 256) {
+    const float a = per_column ? absmax[n] : g;
+    absmax[n] = a;
+    scale[n] = (float)((double)a / 127.0);
+  }
+}
+// Pass 3: word w of row k packs columns 4w..4w+3: byte j = round(x / absmax * 127) & 0xff with the arithmetic of
+// the JavaScript expression: double precision, Math.round = floor(x + 0.5) (:36-42). A zero column packs zeros.
+__global__ void int8_pack_kernel(const float *__restrict__ w, const float *__restrict__ absmax, int K, int N,
+                                 uint32_t *__restrict__ packed) {
+  const size_t total = (size_t)K * (N >> 2);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t k = i / (N >> 2);
+    const int n = (int)(i - k * (N >> 2)) * 4;
+    const float4 x = *reinterpret_cast<const float4 *>(w + k * N + n);
+    const float4 a = *reinterpret_cast<const float4 *>(absmax + n);
+    const float xv[4] = {x.x, x.y, x.z, x.w}, av[4] = {a.x, a.y, a.z, a.w};
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      int q = 0;
+      if (av[j] > 0.f) q = (int)floor(__dmul_rn(__ddiv_rn((double)xv[j], (double)av[j]), 127.0) + 0.5);
+      word |= ((uint32_t)q & 0xffu) << (8 * j);
+    }
+    packed[i] = word;
+  }
+}
+
 // M <= 16 rows. Lane owns 4*VEC consecutive columns (VEC 32-bit words per load: VEC = 4 is a 128-bit load);
 // a warp covers 128*VEC columns of one k row; 8 warps x gridDim.y CTAs split K.
 // part: [gridDim.y][M][N] partial sums, summed (and scaled) by gemv_kn_reduce_kernel.

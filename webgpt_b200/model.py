@@ -82,7 +82,7 @@ class Session:
 
 class GPT:
     def __init__(self, folder, type="bpe", *, weights=None, params=None, fused=True, device_ordinal=0,
-                 tokenizer=None):
+                 tokenizer=None, weight_layout=None):
         """model.js:2-21. `folder` is a weight directory in the reference's format; alternatively pass
         `params` + `weights` (a dict of state-dict-keyed arrays, e.g. from synth.make_weights)."""
         self.folder = folder
@@ -100,6 +100,7 @@ class GPT:
         self.externalBuffer = None
         self.unloadDeletionStack = []
         self._weights = weights
+        self._weight_layout = weight_layout  # None: what params_gpt.json says ("in_out" when it says nothing)
         self._fused = fused
         self._ordinal = device_ordinal
         self.model_handle = None
@@ -250,9 +251,19 @@ class GPT:
 
     # ------------------------------------------------------------------ loading
     def _fetch(self, folder, key):
+        """One tensor in the [in, out] convention of model.js, flattened. Folders in nanoGPT's nn.Linear [out, in]
+        convention (condensed/condensed.js:1765-1784) are transposed here, as that loader does; bias-free
+        checkpoints have no bias files and read as zeros (condensed/condensed.js:1762-1782, model.js:322)."""
         if self._weights is not None:
             return np.ascontiguousarray(self._weights[key], dtype=np.float32).ravel()
-        return G.fetchBin(os.path.join(folder, f"{key}_gpt.bin"))
+        path = os.path.join(folder, f"{key}_gpt.bin")
+        shape = synth.tensor_shape(self.params, key)
+        if key.endswith(".bias") and not self.params.get("bias", True) and not os.path.exists(path):
+            return np.zeros(shape, np.float32).ravel()
+        data = G.fetchBin(path)
+        if self.params.get("weight_layout", "in_out") == "out_in" and len(shape) == 2 and ".h." in key:
+            data = np.ascontiguousarray(data.reshape(shape[1], shape[0]).T).ravel()
+        return data
 
     def loadModel(self, folder):
         """model.js:270-287."""
@@ -291,6 +302,10 @@ class GPT:
             # (block_size, as condensed/condensed.js:1726 reads it)
             if "n_ctx" not in params:
                 params["n_ctx"] = params.get("n_positions", params.get("block_size"))
+            if self._weight_layout is not None:
+                params["weight_layout"] = self._weight_layout
+            if params.get("weight_layout", "in_out") not in ("in_out", "out_in"):
+                raise ValueError("Model load failed: weight_layout must be 'in_out' or 'out_in'.")
         if params["n_embd"] % 4 != 0:
             raise ValueError("Model load failed: n_embd must be divisible by 4.")
         if params["n_embd"] % params["n_head"] != 0:
