@@ -484,8 +484,9 @@ static bool gemv_block_plan(const wgpt_device *dev, int M, int K, int N, bool la
   int w = 1;
   while (c * w < 2 * nw0 && w < 8 && (K / 4) / (w * 2) >= 32) w *= 2;
   const int nw = kBlockGemvThreads / 32;
-  size_t red = (size_t)(c * w > nw ? c * w : nw) * M;
-  size_t bytes = ((size_t)c * K + (size_t)M * K * (layernorm ? 2 : 1) + ((red + 3) & ~size_t(3))) * 4 + 16;
+  size_t red = M > 4 ? (size_t)nw * c * M : (size_t)(c * w > nw ? c * w : nw) * M;
+  const size_t row = (size_t)K + (M > 4 ? 4 : 0);  // input rows are padded by one float4 in the rows-in-lanes form
+  size_t bytes = ((size_t)c * K + (size_t)M * row * (layernorm ? 2 : 1) + ((red + 3) & ~size_t(3))) * 4 + 16;
   if (bytes > dev->smem_optin - 2048) return false;
   *cols = c;
   *wk = w;

@@ -241,26 +241,78 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
 template <int M>
 __device__ __forceinline__ void cta_layernorm_rows(const float *raw, float *normed, int K,
                                                    const float *__restrict__ gamma, const float *__restrict__ beta,
-                                                   float4 g_first, float4 b_first) {
+                                                   float4 g_first, float4 b_first, int rs4) {
+  // rs4: row stride of raw and normed in float4 (K/4, or more when the rows are padded against bank conflicts)
   const int tid = threadIdx.x, lane = tid & 31;
   const int K4 = K >> 2;
   const float4 *x4 = reinterpret_cast<const float4 *>(raw);
   float4 *o4 = reinterpret_cast<float4 *>(normed);
   const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
   const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+  if (M > 1) {
+    // Several rows: the warps share them (warp w takes rows w, w + warps, ...), each computing the statistics of
+    // its row once and writing the normalised row itself. With every warp doing every row the cost grew with M
+    // (28 us against 7 us for an eight-row QKV product).
+    const int warp = tid >> 5, nw = (int)blockDim.x >> 5;
+    // gamma and beta of this lane's first eight positions, requested before the statistics so that their L2
+    // latency overlaps them (loaded one by one inside the last loop they cost a round trip per position)
+    constexpr int GP = 8;
+    float4 gpre[GP], bpre[GP];
+    if (warp < M) {
+#pragma unroll
+      for (int j = 0; j < GP; j++) {
+        const int i = lane + 32 * j;
+        gpre[j] = i < K4 ? __ldg(g4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        bpre[j] = i < K4 ? __ldg(b4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    for (int m = warp; m < M; m += nw) {
+      float s = 0.f;
+#pragma unroll 4
+      for (int i = lane; i < K4; i += 32) {
+        float4 v = x4[(size_t)m * rs4 + i];
+        s += (v.x + v.y) + (v.z + v.w);
+      }
+      const float mean = warp_sum(s) / (float)K;
+      float q = 0.f;
+#pragma unroll 4
+      for (int i = lane; i < K4; i += 32) {
+        float4 v = x4[(size_t)m * rs4 + i];
+        float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+        q += (a * a + b * b) + (c * c + d * d);
+      }
+      const float rsd = 1.0f / sqrtf(warp_sum(q) / (float)K + 1e-5f);
+#pragma unroll
+      for (int j = 0; j < GP; j++) {
+        const int i = lane + 32 * j;
+        if (i < K4) {
+          const float4 v = x4[(size_t)m * rs4 + i], g = gpre[j], b = bpre[j];
+          o4[(size_t)m * rs4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
+                                               g.z * ((v.z - mean) * rsd) + b.z, g.w * ((v.w - mean) * rsd) + b.w);
+        }
+      }
+      for (int i = lane + 32 * GP; i < K4; i += 32) {
+        const float4 v = x4[(size_t)m * rs4 + i], g = __ldg(g4 + i), b = __ldg(b4 + i);
+        o4[(size_t)m * rs4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
+                                             g.z * ((v.z - mean) * rsd) + b.z, g.w * ((v.w - mean) * rsd) + b.w);
+      }
+    }
+    __syncthreads();
+    return;
+  }
 #pragma unroll
   for (int m = 0; m < M; m++) {
     float s = 0.f;
 #pragma unroll 4
     for (int i = lane; i < K4; i += 32) {
-      float4 v = x4[(size_t)m * K4 + i];
+      float4 v = x4[(size_t)m * rs4 + i];
       s += (v.x + v.y) + (v.z + v.w);
     }
     const float mean = warp_sum(s) / (float)K;
     float q = 0.f;
 #pragma unroll 4
     for (int i = lane; i < K4; i += 32) {
-      float4 v = x4[(size_t)m * K4 + i];
+      float4 v = x4[(size_t)m * rs4 + i];
       float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
       q += (a * a + b * b) + (c * c + d * d);
     }
@@ -268,8 +320,8 @@ __device__ __forceinline__ void cta_layernorm_rows(const float *raw, float *norm
     // multiplying by 1/sd by at most one unit in the last place
     const float rsd = 1.0f / sqrtf(warp_sum(q) / (float)K + 1e-5f);
     for (int i = tid; i < K4; i += (int)blockDim.x) {
-      float4 v = x4[(size_t)m * K4 + i], g = i == tid ? g_first : g4[i], b = i == tid ? b_first : b4[i];
-      o4[(size_t)m * K4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
+      float4 v = x4[(size_t)m * rs4 + i], g = i == tid ? g_first : g4[i], b = i == tid ? b_first : b4[i];
+      o4[(size_t)m * rs4 + i] = make_float4(g.x * ((v.x - mean) * rsd) + b.x, g.y * ((v.y - mean) * rsd) + b.y,
                                            g.z * ((v.z - mean) * rsd) + b.z, g.w * ((v.w - mean) * rsd) + b.w);
     }
   }
@@ -295,12 +347,16 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
                   const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, int cols, int wk,
                   Epilogue epi, int *err, AttnPartials ap) {
   extern __shared__ __align__(128) float smem[];
+  // Rows-in-lanes form (more than four rows, see below): eight lanes read the same float4 position of eight
+  // rows at once, so the rows are padded by one float4 to fall into different banks.
+  constexpr bool kRowsInLanes = M > 4;
+  const int RS4 = (K >> 2) + (kRowsInLanes ? 1 : 0);                      // row stride of xs / xn in float4
   float *wbuf = smem;
   float *xs = wbuf + (size_t)cols * K;                                    // input rows as staged
-  float *xn = gamma != nullptr ? xs + (size_t)M * K : xs;                // normalised rows (LayerNorm only)
-  float *red = xn + (size_t)M * K;
+  float *xn = gamma != nullptr ? xs + (size_t)M * RS4 * 4 : xs;          // normalised rows (LayerNorm only)
+  float *red = xn + (size_t)M * RS4 * 4;
   constexpr int NT = kBlockGemvThreads, NW = NT / 32;
-  const int red_floats = (max(cols * wk, NW) * M + 3) & ~3;
+  const int red_floats = ((kRowsInLanes ? NW * cols : max(cols * wk, NW)) * M + 3) & ~3;
   uint64_t *bar = reinterpret_cast<uint64_t *>(red + red_floats);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K4 = K >> 2;
@@ -349,17 +405,28 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     if (ap.part != nullptr) {  // the input rows are attention outputs still split into position slices
 #pragma unroll
       for (int m = 0; m < M; m++)
-        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * K4 + i] = attn_merged_value4(ap, m, 4 * i);
+        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * RS4 + i] = attn_merged_value4(ap, m, 4 * i);
+    } else if (M > 1) {
+      // Every CTA reads the same rows at the same time; starting each CTA at a different offset spreads the
+      // requests over L2 instead of having all SMs ask for the same lines at once.
+      const int total = M * K4;
+      const int rot = (int)(((unsigned)blockIdx.x * 32u * 13u) % (unsigned)total);
+      for (int j = tid; j < total; j += NT) {
+        int idx = j + rot;
+        if (idx >= total) idx -= total;
+        const int m = idx / K4, i = idx - m * K4;
+        xs4w[(size_t)m * RS4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
+      }
     } else {
 #pragma unroll
       for (int m = 0; m < M; m++)
 #pragma unroll 4
-        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * K4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
+        for (int i = tid; i < K4; i += NT) xs4w[(size_t)m * RS4 + i] = __ldcg(x4 + (size_t)m * ldx4 + i);
     }
   }
   __syncthreads();  // also makes the mbarrier initialisation visible to every thread
   trace(2, 2);
-  if (gamma != nullptr) cta_layernorm_rows<M>(xs, xn, K, gamma, beta, g_first, b_first);
+  if (gamma != nullptr) cta_layernorm_rows<M>(xs, xn, K, gamma, beta, g_first, b_first, RS4);
 
   // Bounded wait for the weights. On expiry: flag the error, give the copies one more bounded chance to land
   // (shared memory must not be released under them), and leave without storing.
@@ -374,6 +441,48 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
   trace(2, 4);
   const float4 *w4 = reinterpret_cast<const float4 *>(wbuf);
   const float4 *xs4 = reinterpret_cast<const float4 *>(xn);
+  if (kRowsInLanes) {
+    // More than four rows: a lane is (row slot = lane % 8, one of four K sub-slices = lane / 8) and every warp takes one
+    // K chunk for all of the CTA's columns, eight columns at a time. A weight float4 is then read once per warp
+    // (the eight row lanes share the address) and an input float4 once per column pass; with the K-in-lanes form
+    // used for one row every warp re-read all M rows for every three columns (245 KB of shared-memory reads per
+    // CTA for an eight-row QKV product, 4 us, and 128 registers, which kept the next kernel off the SM).
+    constexpr int CB = 8;
+    const int mrow = lane & 7, ksl = lane >> 3;
+    const int mm = mrow < M ? mrow : M - 1;
+    const int cbeg = (int)(((unsigned)K4 * (unsigned)warp) / NW), cend = (int)(((unsigned)K4 * (unsigned)(warp + 1)) / NW);
+    for (int c0 = 0; c0 < ncol; c0 += CB) {
+      float acc[CB];
+#pragma unroll
+      for (int cc = 0; cc < CB; cc++) acc[cc] = 0.f;
+      for (int i = cbeg + ksl; i < cend; i += 4) {
+        const float4 xv = xs4[(size_t)mm * RS4 + i];
+#pragma unroll
+        for (int cc = 0; cc < CB; cc++) {
+          const int c = c0 + cc < ncol ? c0 + cc : ncol - 1;
+          acc[cc] += dot4(w4[(size_t)c * K4 + i], xv);
+        }
+      }
+#pragma unroll
+      for (int cc = 0; cc < CB; cc++) {
+        float v = acc[cc];
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (ksl == 0 && mrow < M && c0 + cc < ncol) red[((size_t)warp * cols + c0 + cc) * M + mrow] = v;
+      }
+    }
+    trace(2, 5);
+    __syncthreads();
+    for (int o = tid; o < ncol * M; o += NT) {  // the K chunks of an output in warp order
+      const int cc = o / M, m = o - cc * M;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; w++) v += red[((size_t)w * cols + cc) * M + m];
+      epi_store(epi, v, m, col0 + cc);
+    }
+    trace(2, 6);
+    return;
+  }
   constexpr int NB = 3;
   for (int it0 = warp; it0 < items; it0 += NW * NB) {
     int c[NB];
@@ -393,7 +502,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     for (int i = beg + lane; i < end; i += 32) {
       float4 xv[M];
 #pragma unroll
-      for (int m = 0; m < M; m++) xv[m] = xs4[(size_t)m * K4 + i];
+      for (int m = 0; m < M; m++) xv[m] = xs4[(size_t)m * RS4 + i];
 #pragma unroll
       for (int b = 0; b < NB; b++) {
         if (valid[b]) {
