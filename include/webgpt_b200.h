@@ -127,6 +127,16 @@ int32_t wgpt_matmul_nk(wgpt_device *dev, int32_t rows, int32_t cols, int32_t sha
  * model-level calls do this themselves; the per-operator calls only enqueue. */
 int32_t wgpt_device_check(wgpt_device *dev);
 
+/* Diagnostic, no counterpart in the reference: runs a one-thread kernel whose bounded mbarrier wait (the wait every
+ * bulk-copy kernel of this library uses) cannot complete within `polls` polls because the barrier is armed for more
+ * bytes than the first copy delivers. The kernel then takes the library's expiry path: it sets the device error
+ * word, supplies the missing bytes, completes a second bounded wait and returns. *first_wait_completed is 0 when
+ * the wait ran out (expected), *drain_wait_completed 1 when the drain succeeded. The next wgpt_device_check
+ * reports WGPT_ERR_TIMEOUT once and clears it; the device stays usable. Nothing faults and nothing waits without
+ * a limit. polls in 1..1024. */
+int32_t wgpt_device_probe_wait_expiry(wgpt_device *dev, uint32_t polls, int32_t *first_wait_completed,
+                                      int32_t *drain_wait_completed);
+
 /* No counterpart in the reference. The same product as wgpt_matmul for 1..8 rows, for callers that must not
  * trigger a device allocation: an inference server that has handed all of HBM to its own arena and treats any
  * later cudaMalloc as a budget violation, a latency-critical decode loop (cudaMalloc can serialise against every
@@ -239,6 +249,15 @@ int32_t wgpt_model_run(wgpt_session *session, const uint32_t *idx_host, int32_t 
  * (model.js:69) each step recomputes the slid window, as the reference does. */
 int32_t wgpt_generate_greedy(wgpt_session *session, const uint32_t *prompts_host, int32_t n_prompt, int32_t n_new,
                              uint32_t *new_ids_host);
+
+/* GPT.generate for independent sequences spread over several GPUs (each sequence has its own ids, cache and
+ * logits; GPT.run has no cross-sequence state, model.js:104-268): sessions[i] is a session of n_seq_i sequences on
+ * its own device (one wgpt_device + wgpt_model per GPU, weights replicated). prompts_host is
+ * [sum of n_seq_i, n_prompt] in session order, new_ids_host [sum of n_seq_i, n_new] likewise. One host thread per
+ * session runs wgpt_generate_greedy on its block; all are joined before the call returns. Nothing is exchanged
+ * between devices. Two sessions must not share a wgpt_device handle. */
+int32_t wgpt_generate_greedy_sharded(wgpt_session **sessions, int32_t n_sessions, const uint32_t *prompts_host,
+                                     int32_t n_prompt, int32_t n_new, uint32_t *new_ids_host);
 
 /* The three stages of wgpt_generate_greedy as separate calls, for callers that keep prompts resident or want to
  * overlap: set_prompts uploads [n_seq, n_prompt] ids; generate only enqueues the whole greedy loop (no copy and,

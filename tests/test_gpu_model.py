@@ -348,6 +348,49 @@ def test_load_linear_layout_and_bias_free_folder(tmp_path):
         b.destroy()
 
 
+def test_sharded_generation_inside_the_library_equals_unsharded(oracle):
+    """wgpt_generate_greedy_sharded: the sequences of one call split over several device handles, one host thread
+    each, joined inside the library. With one GPU present the handles sit on the same GPU (two streams); with more,
+    on different GPUs. The gathered ids must equal the unsharded ids and the oracle's."""
+    import ctypes as C
+    from webgpt_b200 import WgptError, _lib
+    from webgpt_b200.sharding import MultiGPT
+    params = synth.CONFIGS["small"]
+    w = synth.make_weights(params, seed=6, std=0.1, ln_random=True)
+    n_seq, n_prompt, n_new = 11, 9, 10
+    prompts = np.stack([synth.make_tokens(params["vocab_size"], n_prompt, seed=20, stream=i) for i in range(n_seq)])
+    n_dev = 1
+    try:
+        import torch
+        n_dev = max(1, torch.cuda.device_count())
+    except Exception:
+        pass
+    devices = [i % n_dev for i in range(max(2, min(n_dev, 4)))]
+    multi = MultiGPT(params, w, devices)
+    single = make_gpt(params, w)
+    try:
+        got = multi.generate_greedy(prompts, n_new)
+        want = single.session(n_seq).generate_greedy(prompts, n_new)
+        assert np.array_equal(got, want)
+        m = oracle.Model(params, synth.weight_list(params, w))
+        for i in (0, 5, n_seq - 1):
+            assert np.array_equal(got[i], m.generate_greedy(prompts[i], n_new)[n_prompt:])
+        # two sessions on one device handle are refused
+        g = multi.gpts[0]
+        from webgpt_b200.model import Session
+        s1, s2 = Session(g, 1), Session(g, 1)
+        arr = (C.c_void_p * 2)(s1.handle, s2.handle)
+        out = np.empty((2, 2), np.uint32)
+        with pytest.raises(WgptError) as e:
+            _lib.call("wgpt_generate_greedy_sharded", arr, 2, prompts.ctypes.data, n_prompt, 2, out.ctypes.data)
+        assert e.value.code == _lib.ERR_ARG
+        s1.destroy()
+        s2.destroy()
+    finally:
+        multi.destroy()
+        single.destroy()
+
+
 def test_whole_token_decode_kernel_opt_in(oracle, monkeypatch):
     """WGPT_PERSISTENT=1 routes single-sequence decode through decode_persistent_kernel (grid barriers instead
     of kernel boundaries); same tokens and logits as the oracle."""

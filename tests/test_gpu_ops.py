@@ -318,3 +318,31 @@ def test_int8_quantize_bit_exact(dev, oracle, K, N, per_column):
         got = o_d.read(np.float32, 2 * N).reshape(2, N)
         assert rel_err(got, oracle.int8_matmul(A, ref_q, ref_s, N)) < TOL
         assert np.max(np.abs(got - A @ w)) < 0.1     # the prototype's acceptance rule, other/int8-gemm.js:321
+
+
+def test_bounded_wait_expiry_reports_timeout_and_device_survives(oracle):
+    """A bounded device-side wait driven to its limit: the probe kernel's mbarrier is armed for more bytes than its
+    first copy delivers, so the wait gives up after a handful of polls, the kernel flags the error word, drains
+    with a second bounded wait and returns. wgpt_device_check then reports WGPT_ERR_TIMEOUT exactly once, and the
+    same device computes a correct product afterwards."""
+    import ctypes as C
+    from webgpt_b200 import Device, WgptError, _lib
+    dev = Device(0)
+    try:
+        first, drain = C.c_int32(-1), C.c_int32(-1)
+        _lib.call("wgpt_device_probe_wait_expiry", dev.handle, 4, C.byref(first), C.byref(drain))
+        assert first.value == 0      # the wait ran out
+        assert drain.value == 1      # the drain wait completed: no copy was left in flight
+        with pytest.raises(WgptError) as e:
+            _lib.call("wgpt_device_check", dev.handle)
+        assert e.value.code == _lib.ERR_TIMEOUT and "did not complete in time" in e.value.message
+        _lib.call("wgpt_device_check", dev.handle)   # reported once, then clear
+        rng = np.random.default_rng(13)
+        A = rng.standard_normal((1, 768), dtype=np.float32)
+        W = (rng.standard_normal((768, 768), dtype=np.float32) * 0.05).astype(np.float32)
+        a_d, w_d, y_d = dev.tensor(A), dev.tensor(np.ascontiguousarray(W.T)), dev.buffer(768 * 4)
+        _lib.call("wgpt_matmul_nk", dev.handle, 1, 768, 768, a_d.ptr, w_d.ptr, None, y_d.ptr)   # bulk-copy GEMV
+        _lib.call("wgpt_device_check", dev.handle)
+        assert rel_err(y_d.read(np.float32, 768).reshape(1, 768), oracle.matmul(A, W)) < TOL
+    finally:
+        dev.destroy()

@@ -61,6 +61,7 @@ SIGNATURES = {
     "wgpt_matmul": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_matmul_nk": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_device_check": [vp],
+    "wgpt_device_probe_wait_expiry": [vp, C.c_uint32, C.POINTER(i32), C.POINTER(i32)],
     "wgpt_matmul_static": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_residual": [vp, i32, i32, vp, vp, vp],
     "wgpt_layernorm": [vp, i32, i32, vp, vp, vp, vp],
@@ -82,6 +83,7 @@ SIGNATURES = {
     "wgpt_session_forward": [vp, vp, i32, vp],
     "wgpt_model_run": [vp, vp, i32, vp],
     "wgpt_generate_greedy": [vp, vp, i32, i32, vp],
+    "wgpt_generate_greedy_sharded": [vpp, i32, vp, i32, i32, vp],
     "wgpt_session_set_prompts": [vp, vp, i32],
     "wgpt_session_generate": [vp, i32],
     "wgpt_session_get_new_ids": [vp, i32, vp],

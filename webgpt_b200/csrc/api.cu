@@ -11,6 +11,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "attention.cuh"
@@ -871,6 +872,25 @@ WGPT_EXPORT int32_t wgpt_device_check(wgpt_device *dev) {
   TRY(use(dev));
   NOT_RECORDING(dev, "wgpt_device_check");
   return check_err_word(dev, "wgpt_device_check");
+}
+
+WGPT_EXPORT int32_t wgpt_device_probe_wait_expiry(wgpt_device *dev, uint32_t polls, int32_t *first_wait_completed,
+                                                  int32_t *drain_wait_completed) {
+  TRY(use(dev));
+  NOT_RECORDING(dev, "wgpt_device_probe_wait_expiry");
+  REQUIRE(first_wait_completed && drain_wait_completed, WGPT_ERR_ARG, "null argument");
+  REQUIRE(polls >= 1 && polls <= 1024, WGPT_ERR_ARG, "polls must be in 1..1024");
+  TRY(scratch_reserve(dev, 256));
+  float *src = static_cast<float *>(dev->scratch);
+  int *obs = reinterpret_cast<int *>(src + 16);
+  CK(cudaMemsetAsync(src, 0, 128, dev->stream));
+  LAUNCH(dev, wait_expiry_probe_kernel, 1, 32, 0, (const float *)src, dev->d_err, polls, obs);
+  int h[2] = {-1, -1};
+  CK(cudaMemcpyAsync(h, obs, sizeof h, cudaMemcpyDeviceToHost, dev->stream));
+  CK(cudaStreamSynchronize(dev->stream));
+  *first_wait_completed = h[0];
+  *drain_wait_completed = h[1];
+  return WGPT_OK;
 }
 
 WGPT_EXPORT int32_t wgpt_residual(wgpt_device *dev, int32_t rows, int32_t cols, const float *a, const float *b,
@@ -2115,6 +2135,42 @@ WGPT_EXPORT int32_t wgpt_generate_sample(wgpt_session *s, const uint32_t *prompt
   TRY(set_prompts(s, prompts_host, n_prompt));
   TRY(wgpt_session_generate_sample(s, n_new, top_k, temperature, uniforms_host));
   return wgpt_session_get_new_ids(s, n_new, new_ids_host);
+}
+
+// Sequence sharding inside the library: sessions[i] holds n_seq_i sequences on its own device (weights are
+// replicated, one model per device); prompts_host is [sum n_seq_i, n_prompt] in session order and new_ids_host
+// [sum n_seq_i, n_new] likewise. One host thread per session runs wgpt_generate_greedy on its block; all are joined
+// before the call returns. No data crosses between devices: the path has no exchange step.
+WGPT_EXPORT int32_t wgpt_generate_greedy_sharded(wgpt_session **sessions, int32_t n_sessions,
+                                                 const uint32_t *prompts_host, int32_t n_prompt, int32_t n_new,
+                                                 uint32_t *new_ids_host) {
+  REQUIRE(sessions && prompts_host && new_ids_host, WGPT_ERR_ARG, "null argument");
+  REQUIRE(n_sessions >= 1, WGPT_ERR_SHAPE, "n_sessions must be at least 1");
+  REQUIRE(n_prompt >= 1 && n_new >= 1, WGPT_ERR_SHAPE, "n_prompt and n_new must be at least 1");
+  for (int i = 0; i < n_sessions; i++) {
+    REQUIRE(sessions[i] != nullptr, WGPT_ERR_ARG, "session %d is null", i);
+    for (int j = 0; j < i; j++)
+      REQUIRE(sessions[j]->m->dev != sessions[i]->m->dev, WGPT_ERR_ARG,
+              "sessions %d and %d share a device handle: a device handle may be driven by one thread at a time", j, i);
+  }
+  std::vector<int32_t> rc(n_sessions, WGPT_OK);
+  std::vector<std::string> msg(n_sessions);
+  std::vector<std::thread> workers;
+  size_t row = 0;
+  for (int i = 0; i < n_sessions; i++) {
+    wgpt_session *s = sessions[i];
+    const uint32_t *p = prompts_host + row * (size_t)n_prompt;
+    uint32_t *o = new_ids_host + row * (size_t)n_new;
+    row += (size_t)s->n_seq;
+    workers.emplace_back([=, &rc, &msg] {
+      rc[i] = wgpt_generate_greedy(s, p, n_prompt, n_new, o);
+      if (rc[i] != WGPT_OK) msg[i] = g_err;  // g_err is per thread: carry the message back
+    });
+  }
+  for (auto &t : workers) t.join();
+  for (int i = 0; i < n_sessions; i++)
+    if (rc[i] != WGPT_OK) return fail(rc[i], "session %d: %s", i, msg[i].c_str());
+  return WGPT_OK;
 }
 
 // Per-operator form of the sampling step: one pick per row of logits[n_rows, V] (all device pointers).

@@ -240,4 +240,24 @@ __global__ void heatmap_kernel(const float *__restrict__ buf, uchar4 *__restrict
   }
 }
 
+// Diagnostic: drives the bounded mbarrier wait the bulk-copy kernels use to its limit, safely. The barrier is armed
+// for 32 bytes but only 16 are copied at first, so its phase cannot complete and mbar_wait gives up after `polls`
+// polls; the kernel then does what the product kernels do on expiry: it sets the device error word to 2, lets the
+// outstanding copy finish (here by supplying the missing 16 bytes, after which a second bounded wait succeeds) and
+// returns. Nothing spins without a limit and nothing faults; the context stays usable.
+__global__ void wait_expiry_probe_kernel(const float *__restrict__ src16, int *err, uint32_t polls, int *observed) {
+  __shared__ __align__(16) float buf[8];
+  __shared__ uint64_t bar;
+  if (threadIdx.x != 0) return;
+  mbar_init(&bar, 1);
+  mbar_expect_tx(&bar, 32);
+  bulk_g2s(buf, src16, 16, &bar);
+  const bool first = mbar_wait(&bar, 0, polls);
+  if (!first) atomicExch(err, 2);
+  bulk_g2s(buf + 4, src16, 16, &bar);                 // the rest of the bytes the barrier was armed for
+  const bool second = mbar_wait(&bar, 0, 1u << 22);   // drain: bounded as well
+  observed[0] = first ? 1 : 0;
+  observed[1] = second ? 1 : 0;
+}
+
 }  // namespace wgpt

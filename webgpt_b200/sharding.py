@@ -54,3 +54,38 @@ def generate_sharded(generate_block, prompts, n_new, dist=None):
     a, b = shard_range(prompts.shape[0], world, rank)
     local = generate_block(prompts[a:b], n_new) if b > a else np.empty((0, n_new), np.uint32)
     return gather_ids(local, prompts.shape[0], dist if world > 1 else None)
+
+
+class MultiGPT:
+    """The same model on several GPUs of one process (weights replicated), for generating many independent
+    sequences with one call: sequences are split into contiguous blocks (shard_range), one block per device, and
+    wgpt_generate_greedy_sharded runs one host thread per device inside the library."""
+
+    def __init__(self, params, weights, devices):
+        from .model import GPT
+        self.gpts = [GPT(None, params=params, weights=weights, device_ordinal=d) for d in devices]
+        for g in self.gpts:
+            g.initialize()
+        self.params = self.gpts[0].params
+
+    def generate_greedy(self, prompts, n_new):
+        import ctypes as C
+        from . import _lib
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint32)
+        n_seq, n_prompt = prompts.shape
+        world = len(self.gpts)
+        sessions = []
+        for r, g in enumerate(self.gpts):
+            a, b = shard_range(n_seq, world, r)
+            if b > a:
+                sessions.append(g.session(b - a))
+        arr = (C.c_void_p * len(sessions))(*[s.handle for s in sessions])
+        out = np.empty((n_seq, n_new), np.uint32)
+        _lib.call("wgpt_generate_greedy_sharded", arr, len(sessions), prompts.ctypes.data, n_prompt, n_new,
+                  out.ctypes.data)
+        return out
+
+    def destroy(self):
+        for g in self.gpts:
+            g.destroy()
+        self.gpts = []
