@@ -44,9 +44,10 @@ enum {
   WGPT_ERR_ARG = -8          /* null pointer, bad enum value, id out of range */
 };
 
-/* Arithmetic used by matrix products with more than 8 rows against weights in the model's [N,K] layout (prefill,
- * batched decode, wgpt_matmul_nk). Products with up to 8 rows, and wgpt_matmul on reference-layout weights, always
- * run in FP32 on the CUDA cores. A new device starts in WGPT_PRECISION_TF32X3. */
+/* Arithmetic used by matrix products with more than 8 rows (prefill, batched decode, wgpt_matmul_nk; wgpt_matmul and
+ * wgpt_attention on reference-layout weights from 32 rows on, through a transposed copy of the weight in the
+ * workspace). Products with up to 8 rows always run in FP32 on the CUDA cores. A new device starts in
+ * WGPT_PRECISION_TF32X3. */
 enum {
   WGPT_PRECISION_FP32 = 0,   /* FP32 FMA on the CUDA cores */
   WGPT_PRECISION_TF32X3 = 1, /* tensor cores, three TF32 products per FP32 product (error 1e-6..2e-5, growing with K) */

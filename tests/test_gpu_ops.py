@@ -7,6 +7,7 @@ from conftest import load_golden, rel_err
 pytestmark = pytest.mark.gpu
 
 TOL = 2e-5  # relative, FP32 paths (the reference's own bound is 1e-3 absolute, validation.js:216)
+TOL_X3 = 5e-5  # products of 32 rows and more run on the tensor cores in 3xTF32 (see test_gpu_tensorcore.py)
 
 
 @pytest.fixture(scope="module")
@@ -33,7 +34,8 @@ def run(inst):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 8, 8), (1, 768, 2304), (3, 12, 16), (4, 384, 384), (8, 3072, 768),
-                                   (15, 128, 384), (33, 384, 1536), (256, 768, 768), (1, 1600, 6400)])
+                                   (15, 128, 384), (33, 384, 1536), (256, 768, 768), (1, 1600, 6400),
+                                   (1024, 768, 2304), (100, 1600, 72)])
 def test_matmul(dev, ops, oracle, M, K, N):
     rng = np.random.default_rng(M * 1000 + N)
     A = rng.standard_normal((M, K), dtype=np.float32)
@@ -41,7 +43,7 @@ def test_matmul(dev, ops, oracle, M, K, N):
     b = rng.standard_normal(N, dtype=np.float32)
     out = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(b)))
     got = out.read(np.float32, M * N).reshape(M, N)
-    assert rel_err(got, oracle.matmul(A, B, b)) < TOL
+    assert rel_err(got, oracle.matmul(A, B, b)) < (TOL if M < 32 else TOL_X3)
     # deterministic: the split-K sums are added in a fixed order
     out2 = run(ops.FastMatMulBlock.newInstance(M, N, K, dev.tensor(A), dev.tensor(B), dev.tensor(b)))
     assert np.array_equal(out2.read(np.float32, M * N).reshape(M, N), got)
@@ -123,7 +125,7 @@ def test_attention(dev, ops, oracle, T, E, H):
                                                t(b[2]), t(W[3]), t(b[3]), ops.FastMatMulBlock, ops.SoftmaxBlock)
     got = run(inst).read(np.float32, T * E).reshape(T, E)
     ref = oracle.attention(x, H, np.float32(scale), W[0], b[0], W[1], b[1], W[2], b[2], W[3], b[3])
-    assert rel_err(got, ref) < TOL
+    assert rel_err(got, ref) < (TOL if T < 32 else TOL_X3)
 
 
 def test_attention_known_answer(dev, ops):

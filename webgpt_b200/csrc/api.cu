@@ -771,12 +771,27 @@ static int32_t gemv_kn_with_scratch(wgpt_device *dev, int M, const float *x, con
   return WGPT_OK;
 }
 
+// out = A[M,K] . W[K,N] on the tensor cores: wt (K*N floats of workspace) receives W transposed to [N,K].
+static int32_t gemm_kn_via_transpose(wgpt_device *dev, const float *A, size_t lda, const float *W, int M, int K, int N,
+                                     const Epilogue &epi, float *wt) {
+  dim3 tg((unsigned)((N + 31) / 32), (unsigned)((K + 31) / 32));
+  LAUNCH(dev, transpose_kernel, tg, dim3(32, 8), 0, W, wt, K, N);
+  // the transposed copy was written by the kernel just before: no reads of it ahead of the dependency wait
+  return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, lda, wt, M, K, N, epi, nullptr, false);
+}
+
 // The reference-layout matmul used by the per-operator API: W is [K,N].
 static int32_t matmul_kn(wgpt_device *dev, int M, int K, int N, const float *in, const float *W, const Epilogue &epi) {
   if (M <= 8) {
     int ksplit = kn_ksplit(dev, M, K, (N + 127) / 128);
     TRY(scratch_reserve(dev, (size_t)ksplit * M * N * 4));
     return gemv_kn_with_scratch(dev, M, in, W, K, N, ksplit, static_cast<float *>(dev->scratch), epi);
+  }
+  if (dev->precision != WGPT_PRECISION_FP32 && M >= 32) {
+    // Tensor cores behind the reference layout: W[K,N] is transposed into the workspace (one pass over the weight,
+    // a few microseconds against a product of more than a hundred) and the [N,K] kernel runs on the copy.
+    TRY(scratch_reserve(dev, (size_t)K * N * 4));
+    return gemm_kn_via_transpose(dev, in, (size_t)K, W, M, K, N, epi, static_cast<float *>(dev->scratch));
   }
   return launch_gemm_simt(dev, false, in, (size_t)K, W, M, K, N, epi);
 }
@@ -1004,12 +1019,14 @@ WGPT_EXPORT int32_t wgpt_attention(wgpt_device *dev, int32_t T, int32_t E, float
   // workspace: q, k, v, o [T,E] + split-K partials
   size_t te = (size_t)T * E;
   int ksplit = T <= 8 ? kn_ksplit(dev, T, E, (E + 127) / 128) : 0;
-  size_t part_floats = (size_t)ksplit * T * E;
+  const bool tc = dev->precision != WGPT_PRECISION_FP32 && T >= 32;
+  size_t part_floats = tc ? (size_t)E * E : (size_t)ksplit * T * E;  // split-K partials, or a transposed weight
   TRY(scratch_reserve(dev, (4 * te + part_floats) * 4));
   float *q = static_cast<float *>(dev->scratch), *k = q + te, *v = k + te, *o = v + te, *part = o + te;
   auto mm = [&](const float *a, const float *W, const float *b, float *dst) -> int32_t {
     Epilogue e = plain_epi(dst, E, b);
     if (T <= 8) return gemv_kn_with_scratch(dev, T, a, W, E, E, ksplit, part, e);
+    if (tc) return gemm_kn_via_transpose(dev, a, (size_t)E, W, T, E, E, e, part);
     return launch_gemm_simt(dev, false, a, (size_t)E, W, T, E, E, e);
   };
   TRY(mm(in, qW, qB, q));
