@@ -811,6 +811,14 @@ static int32_t launch_attn_prefill_t(wgpt_device *dev, const float *q, int ldq, 
 static int32_t launch_attn_prefill(wgpt_device *dev, int hs, const float *q, int ldq, const float *kc, const float *vc,
                                    int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_tok, int n_seq, int H,
                                    const int *pos, float scale) {
+  static const bool tiled64 = [] { const char *ev = getenv("WGPT_ATTN_PREFILL64"); return !(ev && ev[0] == '0'); }();
+  if (hs == 64 && tiled64 && n_tok >= 16 && (ldq % 4) == 0 && (ldkv % 4) == 0 && (ldo % 4) == 0) {
+    const size_t smem = attn_prefill64_smem_bytes();
+    CK(cudaFuncSetAttribute(attn_prefill64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((n_tok + kAttn64Tile - 1) / kAttn64Tile, H, n_seq);
+    LAUNCH(dev, attn_prefill64_kernel, grid, 256, smem, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok, pos, scale);
+    return WGPT_OK;
+  }
 #define CASE(HSV) \
   case HSV: return launch_attn_prefill_t<HSV>(dev, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok, n_seq, H, pos, scale);
   switch (hs) {

@@ -300,4 +300,137 @@ attn_prefill_kernel(const float *__restrict__ q, int ldq, const float *__restric
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Prefill for head size 64 (every GPT-2 size and the char model), register-tiled: a CTA of 256 threads takes 64
+// query rows against key tiles of 64, thread (ty, tx) of a 16 x 16 grid owns queries ty, ty+16, ty+32, ty+48 and
+// keys tx, tx+16, tx+32, tx+48 of the tile for the scores, and the same queries with output dims 4tx..4tx+3 for
+// the values. Q, K, V and the probabilities sit in shared memory in their natural row layout with rows padded to
+// 68 floats; every inner step is 128-bit loads (the four keys of a lane are 16 rows apart, so a quarter-warp's
+// eight addresses fall into different banks): 64 multiply-adds per eight loads, against one per load in the
+// 32 x 32 kernel above. Online softmax per query row across tiles; the 16 lanes that share a row combine their
+// maxima and sums with shuffles. Same mathematics as the chain it replaces (formatQ, fusedWeights with the causal
+// mask, softmax, attentionValues: instructions.js:1101-1214, :593-666); masked keys contribute exactly zero.
+constexpr int kAttn64Tile = 64, kAttn64Ld = 68;
+constexpr size_t attn_prefill64_smem_bytes() { return (size_t)4 * kAttn64Tile * kAttn64Ld * sizeof(float); }
+
+__global__ void __launch_bounds__(256)
+attn_prefill64_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc, const float *__restrict__ vc,
+                      int ldkv, size_t kv_seq_stride, float *__restrict__ out, int ldo, int n_tok,
+                      const int *__restrict__ pos, float scale) {
+  constexpr int HS = 64, T = kAttn64Tile, LD = kAttn64Ld;
+  extern __shared__ __align__(16) float attn_smem[];
+  float *Qs = attn_smem, *Ks = Qs + T * LD, *Vs = Ks + T * LD, *Ps = Vs + T * LD;
+  const int h = blockIdx.y, seq = blockIdx.z, t0 = blockIdx.x * T;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int pos0 = pos ? *pos : 0;
+  const int nq = min(T, n_tok - t0);
+  const int last_key = pos0 + t0 + nq - 1;  // newest key any query of this tile may see
+  int my_pos[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) my_pos[i] = pos0 + t0 + min(ty + 16 * i, nq - 1);  // rows past the end shadow the last one
+
+  for (int idx = tid; idx < T * (HS / 4); idx += 256) {
+    const int r = idx >> 4, c4 = (idx & 15) * 4;
+    const int t = t0 + min(r, nq - 1);
+    *reinterpret_cast<float4 *>(Qs + r * LD + c4) =
+        *reinterpret_cast<const float4 *>(q + ((size_t)seq * n_tok + t) * ldq + h * HS + c4);
+  }
+  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+
+  float m[4], l[4], o[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 4; d++) o[i][d] = 0.f;
+  }
+
+  for (int j0 = 0; j0 <= last_key; j0 += T) {
+    __syncthreads();  // the previous tile's K, V and P are no longer read
+    for (int idx = tid; idx < T * (HS / 4); idx += 256) {
+      const int r = idx >> 4, c4 = (idx & 15) * 4;
+      const int j = min(j0 + r, last_key);
+      *reinterpret_cast<float4 *>(Ks + r * LD + c4) = *reinterpret_cast<const float4 *>(kb + (size_t)j * ldkv + c4);
+      *reinterpret_cast<float4 *>(Vs + r * LD + c4) = *reinterpret_cast<const float4 *>(vb + (size_t)j * ldkv + c4);
+    }
+    __syncthreads();
+    // ---- scores of 4 queries x 4 keys
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int k = 0; k < 4; k++) s[i][k] = 0.f;
+#pragma unroll 4
+    for (int d = 0; d < HS; d += 4) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4 *>(Qs + (ty + 16 * i) * LD + d);
+#pragma unroll
+      for (int k = 0; k < 4; k++) kv[k] = *reinterpret_cast<const float4 *>(Ks + (tx + 16 * k) * LD + d);
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int k = 0; k < 4; k++) s[i][k] += dot4(qv[i], kv[k]);
+    }
+    // ---- online softmax per query row (the 16 lanes with this ty share the row)
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int j = j0 + tx + 16 * k;
+        s[i][k] = (j <= my_pos[i]) ? s[i][k] * scale : -INFINITY;
+        tmax = fmaxf(tmax, s[i][k]);
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+      const float mn = fmaxf(m[i], tmax);
+      const float corr = (m[i] == -INFINITY) ? 0.f : expf(m[i] - mn);
+      float psum = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const float p = (s[i][k] == -INFINITY) ? 0.f : expf(s[i][k] - mn);
+        Ps[(ty + 16 * i) * LD + tx + 16 * k] = p;
+        psum += p;
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
+      if (mn != -INFINITY) {
+        l[i] = l[i] * corr + psum;
+        m[i] = mn;
+      }
+#pragma unroll
+      for (int d = 0; d < 4; d++) o[i][d] *= corr;
+    }
+    __syncthreads();  // the probabilities of the tile are complete
+    // ---- values: 4 queries x 4 output dims
+#pragma unroll 4
+    for (int k = 0; k < T; k += 4) {
+      float4 pv[4], vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) pv[i] = *reinterpret_cast<const float4 *>(Ps + (ty + 16 * i) * LD + k);
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) vv[kk] = *reinterpret_cast<const float4 *>(Vs + (k + kk) * LD + 4 * tx);
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        o[i][0] += pv[i].x * vv[0].x + pv[i].y * vv[1].x + pv[i].z * vv[2].x + pv[i].w * vv[3].x;
+        o[i][1] += pv[i].x * vv[0].y + pv[i].y * vv[1].y + pv[i].z * vv[2].y + pv[i].w * vv[3].y;
+        o[i][2] += pv[i].x * vv[0].z + pv[i].y * vv[1].z + pv[i].z * vv[2].z + pv[i].w * vv[3].z;
+        o[i][3] += pv[i].x * vv[0].w + pv[i].y * vv[1].w + pv[i].z * vv[2].w + pv[i].w * vv[3].w;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = ty + 16 * i;
+    if (r < nq) {
+      const float inv = 1.f / l[i];
+      *reinterpret_cast<float4 *>(out + ((size_t)seq * n_tok + t0 + r) * ldo + h * HS + 4 * tx) =
+          make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
+    }
+  }
+}
+
 }  // namespace wgpt
