@@ -202,6 +202,18 @@ int32_t wgpt_attention(wgpt_device *dev, int32_t seq_length, int32_t n_embd, flo
 int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int32_t N, const float *A, const uint32_t *Bq,
                          const float *scale, float *out);
 
+/* The prototype's load step for a weight that is used many times (it uploads the packed matrix once and then
+ * dispatches against it, other/int8-gemm.js:101-113): the handle owns a copy of Bq [K, N/4] and scale [N] (both
+ * device memory) and, when K % 16 == 0, a re-laid-out copy with each output column's codes contiguous, which the
+ * kernels stream with 128-bit loads. wgpt_int8_matmul_w computes what wgpt_int8_matmul computes, out[M,N] =
+ * A[M,K] . (f32(q) * scale[n]): up to 4 rows in one weight-streaming kernel, more than 16 rows on the tensor cores
+ * (device precision mode), otherwise through wgpt_int8_matmul. */
+typedef struct wgpt_int8_weight wgpt_int8_weight;
+int32_t wgpt_int8_weight_create(wgpt_device *dev, int32_t K, int32_t N, const uint32_t *Bq, const float *scale,
+                                wgpt_int8_weight **out);
+int32_t wgpt_int8_weight_destroy(wgpt_int8_weight *weight);
+int32_t wgpt_int8_matmul_w(wgpt_device *dev, int32_t M, const wgpt_int8_weight *weight, const float *A, float *out);
+
 /* quantizeMatrix (other/int8-gemm.js:25-46) on the device: W is the row-major f32 [K, N] weight; Bq_out receives
  * [K, N/4] words, byte j of word w in row k = round(W[k, 4w+j] / absmax * 127) & 0xff with the JavaScript
  * arithmetic (double precision, Math.round halves toward +infinity, :36-42); scale_out[n] = absmax / 127.

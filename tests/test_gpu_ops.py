@@ -174,6 +174,28 @@ def test_int8_unpack_bit_exact(dev, K):
         assert np.array_equal(got, q[:M].astype(np.float32))
 
 
+@pytest.mark.parametrize("K", [16, 64, 48])
+def test_int8_weight_handle_unpack_bit_exact(dev, K):
+    """The re-laid-out copy of a weight handle (bytes [N, K]) holds exactly the prototype's codes: one-hot
+    activations and unit scales read them back through the streaming kernel (1 to 4 rows), every byte value in every
+    lane of the words."""
+    import ctypes as C
+    from webgpt_b200 import _lib
+    N = 1024
+    vals = np.arange(K * N, dtype=np.int64)
+    q = ((vals * 37 + vals // N) % 256).astype(np.uint8).view(np.int8).reshape(K, N)
+    packed = np.ascontiguousarray(q).view(np.uint32).reshape(K, N // 4)
+    b_d, s_d = dev.tensor(packed), dev.tensor(np.ones(N, np.float32))
+    h = C.c_void_p()
+    _lib.call("wgpt_int8_weight_create", dev.handle, K, N, b_d.ptr, s_d.ptr, C.byref(h))
+    for M, k0 in ((1, 0), (1, K - 1), (3, 5), (4, K - 4), (16, 0)):
+        A = np.eye(K, dtype=np.float32)[k0:k0 + M]
+        out, a_d = dev.buffer(M * N * 4), dev.tensor(A)
+        _lib.call("wgpt_int8_matmul_w", dev.handle, M, h, a_d.ptr, out.ptr)
+        assert np.array_equal(out.read(np.float32, M * N).reshape(M, N), q[k0:k0 + M].astype(np.float32))
+    _lib.call("wgpt_int8_weight_destroy", h)
+
+
 def test_pass_list_graph_replay(dev, ops, oracle):
     """A recorded pass list (wgpt_graph_*) replays to the same bits as eager execution, also after the inputs
     change in place (the recording holds addresses, not values)."""

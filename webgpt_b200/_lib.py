@@ -72,6 +72,9 @@ SIGNATURES = {
     "wgpt_attention": [vp, i32, i32, f32, i32, i32] + [vp] * 10,
     "wgpt_int8_matmul": [vp, i32, i32, i32, vp, vp, vp, vp],
     "wgpt_int8_quantize": [vp, i32, i32, i32, vp, vp, vp],
+    "wgpt_int8_weight_create": [vp, i32, i32, vp, vp, vpp],
+    "wgpt_int8_weight_destroy": [vp],
+    "wgpt_int8_matmul_w": [vp, i32, vp, vp, vp],
     "wgpt_model_create": [vp, C.POINTER(Params), vpp],
     "wgpt_model_set_tensor": [vp, C.c_char_p, vp, u64],
     "wgpt_model_finalize": [vp],

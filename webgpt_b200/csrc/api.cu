@@ -1119,6 +1119,106 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
   return WGPT_OK;
 }
 
+// ---- int8 weight handle: the load step of the prototype (it creates a buffer for the packed matrix and uploads it
+// once, other/int8-gemm.js:101-113, then dispatches against it). The handle owns a re-laid-out copy.
+struct wgpt_int8_weight {
+  wgpt_device *dev;
+  int K, N;
+  uint32_t *words;   // [K, N/4], the prototype's packing (copy)
+  uint8_t *bytes;    // [N, K], K contiguous; nullptr when K % 16 != 0
+  float *scale;      // [N]
+};
+
+WGPT_EXPORT int32_t wgpt_int8_weight_create(wgpt_device *dev, int32_t K, int32_t N, const uint32_t *Bq,
+                                            const float *scale, wgpt_int8_weight **out) {
+  TRY(use(dev));
+  REQUIRE(Bq && scale && out, WGPT_ERR_ARG, "null pointer");
+  *out = nullptr;
+  NOT_RECORDING(dev, "wgpt_int8_weight_create");
+  REQUIRE(K >= 4 && N >= 8 && N % 8 == 0 && K % 4 == 0, WGPT_ERR_SHAPE, "N must be divisible by 8 and K by 4");
+  REQUIRE(aligned16(Bq) && aligned16(scale), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  wgpt_int8_weight *w = new wgpt_int8_weight();
+  w->dev = dev; w->K = K; w->N = N; w->words = nullptr; w->bytes = nullptr; w->scale = nullptr;
+  const size_t nbytes = (size_t)K * N;
+  cudaError_t e = cudaMalloc(&w->words, nbytes);
+  if (e == cudaSuccess) e = cudaMalloc(&w->scale, (size_t)N * 4);
+  if (e == cudaSuccess && K % 16 == 0) e = cudaMalloc(&w->bytes, nbytes);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(w->words, Bq, nbytes, cudaMemcpyDeviceToDevice, dev->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(w->scale, scale, (size_t)N * 4, cudaMemcpyDeviceToDevice, dev->stream);
+  if (e != cudaSuccess) {
+    cudaFree(w->words); cudaFree(w->scale); cudaFree(w->bytes);
+    delete w;
+    return fail(e == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "int8 weight: %s", cudaGetErrorString(e));
+  }
+  if (w->bytes) {
+    dim3 grid((N / 4 + 31) / 32, (K + 31) / 32);
+    LAUNCH(dev, int8_relayout_nk_kernel, grid, 256, 0, (const uint32_t *)w->words, K, N, w->bytes);
+  }
+  CK(cudaStreamSynchronize(dev->stream));
+  *out = w;
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_int8_weight_destroy(wgpt_int8_weight *w) {
+  if (!w) return WGPT_OK;
+  TRY(use(w->dev));
+  NOT_RECORDING(w->dev, "wgpt_int8_weight_destroy");
+  CK(cudaStreamSynchronize(w->dev->stream));
+  cudaFree(w->words); cudaFree(w->scale); cudaFree(w->bytes);
+  delete w;
+  return WGPT_OK;
+}
+
+template <int M>
+static int32_t launch_int8_block_t(wgpt_device *dev, const wgpt_int8_weight *w, const float *A, float *out) {
+  const int K = w->K, N = w->N, nw = kInt8BlockThreads / 32;
+  const int cols = (N + dev->sm_count - 1) / dev->sm_count;
+  int wk = 1;
+  while (cols * wk < 2 * nw && wk < 8 && (K / 16) / (wk * 2) >= 32) wk *= 2;
+  const size_t red = (size_t)(cols * wk > nw ? cols * wk : nw) * M;
+  const size_t smem = (size_t)cols * K + ((size_t)M * K + ((red + 3) & ~size_t(3))) * 4 + 16;
+  if (smem > dev->smem_optin - 2048) return WGPT_ERR_UNSUPPORTED;  // caller falls back (no message: not an error)
+  auto kern = int8_block_gemv_kernel<M>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // the whole carveout, so that the next launch's CTA fits beside this one and fetches its codes early
+  CK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+  LAUNCH_PDL(dev, kern, (N + cols - 1) / cols, kInt8BlockThreads, smem, A, (const uint8_t *)w->bytes,
+             (const float *)w->scale, K, N, cols, wk, out, dev->d_err);
+  return WGPT_OK;
+}
+
+WGPT_EXPORT int32_t wgpt_int8_matmul_w(wgpt_device *dev, int32_t M, const wgpt_int8_weight *w, const float *A,
+                                       float *out) {
+  TRY(use(dev));
+  REQUIRE(w && A && out, WGPT_ERR_ARG, "null pointer");
+  REQUIRE(w->dev == dev, WGPT_ERR_ARG, "the weight belongs to another device handle");
+  REQUIRE(M >= 1, WGPT_ERR_SHAPE, "empty int8 matmul");
+  REQUIRE(aligned16(A) && aligned16(out), WGPT_ERR_ALIGN, "buffers must be 16-byte aligned");
+  const int K = w->K, N = w->N;
+  if (w->bytes != nullptr && M <= 4) {
+    int32_t rc = WGPT_ERR_UNSUPPORTED;
+    switch (M) {
+      case 1: rc = launch_int8_block_t<1>(dev, w, A, out); break;
+      case 2: rc = launch_int8_block_t<2>(dev, w, A, out); break;
+      case 3: rc = launch_int8_block_t<3>(dev, w, A, out); break;
+      case 4: rc = launch_int8_block_t<4>(dev, w, A, out); break;
+    }
+    if (rc != WGPT_ERR_UNSUPPORTED) return rc;
+  }
+  if (w->bytes != nullptr && M > 16 && dev->precision != WGPT_PRECISION_FP32) {
+    // many rows: the codes are expanded to an FP32 [N,K] weight in the workspace (exact; one coalesced pass) and the
+    // tcgen05 product runs on it with the scales in its epilogue
+    TRY(scratch_reserve(dev, (size_t)N * K * 4));
+    float *wt = static_cast<float *>(dev->scratch);
+    const size_t n16 = (size_t)N * K / 16;
+    LAUNCH(dev, int8_expand_bytes_kernel, grid_for(n16, 256, dev->sm_count), 256, 0, (const uint8_t *)w->bytes, n16, wt);
+    Epilogue e = plain_epi(out, N, nullptr);
+    e.colscale = w->scale;
+    return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false);
+  }
+  return wgpt_int8_matmul(dev, M, K, N, A, w->words, w->scale, out);
+}
+
 // ------------------------------------------------------------------------------------------ model
 struct LayerWeights {
   float *ln1_g, *ln1_b, *wqkv_t, *bqkv, *wo_t, *bo, *ln2_g, *ln2_b, *wfc_t, *bfc, *wpr_t, *bpr;
