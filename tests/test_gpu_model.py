@@ -389,24 +389,3 @@ def test_sharded_generation_inside_the_library_equals_unsharded(oracle):
     finally:
         multi.destroy()
         single.destroy()
-
-
-def test_whole_token_decode_kernel_opt_in(oracle, monkeypatch):
-    """WGPT_PERSISTENT=1 routes single-sequence decode through decode_persistent_kernel (grid barriers instead
-    of kernel boundaries); same tokens and logits as the oracle."""
-    monkeypatch.setenv("WGPT_PERSISTENT", "1")
-    g, params, w, gpt = golden_model("gpt2_small.npz")
-    try:
-        n_prompt = len(g["prompt"])
-        n_new = len(g["history"]) - n_prompt
-        from webgpt_b200 import _lib
-        before = gpt.device.launch_count()
-        got = gpt.session().generate_greedy(g["prompt"], n_new)[0]
-        launches = gpt.device.launch_count() - before
-        assert np.array_equal(got, g["history"][n_prompt:])
-        assert launches < 60          # prefill kernels + one cooperative launch, not 62 per token
-        m = oracle.Model(params, synth.weight_list(params, w))
-        long = m.generate_greedy(g["prompt"], 25)[n_prompt:]
-        assert np.array_equal(gpt.session().generate_greedy(g["prompt"], 25)[0], long)
-    finally:
-        gpt.destroy()

@@ -17,7 +17,6 @@
 #include "attention.cuh"
 #include "common.cuh"
 #include "decode_fused.cuh"
-#include "decode_persistent.cuh"
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
@@ -77,10 +76,11 @@ struct wgpt_device {
   size_t tc_scratch_bytes;
   bool pdl;       // launch the decode-chain kernels with programmatic dependent launch (WGPT_PDL=0 turns it off)
   bool graphs;    // replay decode steps as a CUDA graph (WGPT_GRAPH=0 turns it off)
-  bool persistent;  // single-sequence decode through decode_persistent_kernel (WGPT_PERSISTENT=1 turns it on)
   bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
   uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
+  unsigned int *d_work;  // two counters of gemv_loop_kernel (left zero by every launch)
+  bool loop_gemv;     // products against matrices larger than L2 through gemv_loop_kernel (WGPT_LOOP_GEMV=0: off)
   bool fused_decode;  // single-sequence decode with two kernels per block (WGPT_FUSED_DECODE=0 turns it off)
 };
 
@@ -210,22 +210,25 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->scratch_cap = 0;
   dev->scratch_gen = 0;
   dev->d_err = nullptr;
+  dev->d_work = nullptr;
   const char *ev = getenv("WGPT_PDL");
   dev->pdl = !(ev && ev[0] == '0');
   ev = getenv("WGPT_GRAPH");
   dev->graphs = !(ev && ev[0] == '0');
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
-  ev = getenv("WGPT_PERSISTENT");
-  dev->persistent = ev && ev[0] == '1';  // measured slower than the kernel chain on B200, so opt-in
   ev = getenv("WGPT_FUSED_DECODE");
   dev->fused_decode = !(ev && ev[0] == '0');
+  ev = getenv("WGPT_LOOP_GEMV");
+  dev->loop_gemv = !(ev && ev[0] == '0');
   dev->capturing = false;
   dev->capture_launch0 = 0;
   cudaError_t e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
   dev->tc_scratch = nullptr;
   dev->tc_scratch_bytes = size_t(64) << 20;
   if (e == cudaSuccess) e = cudaMalloc(&dev->d_err, sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&dev->d_work, 2 * sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_work, 0, 2 * sizeof(unsigned int), dev->stream);
   if (e == cudaSuccess) e = cudaMalloc(&dev->tc_scratch, dev->tc_scratch_bytes);
   if (e == cudaSuccess) e = cudaMemsetAsync(dev->d_err, 0, sizeof(int), dev->stream);
   if (e != cudaSuccess) {
@@ -241,6 +244,7 @@ WGPT_EXPORT int32_t wgpt_device_destroy(wgpt_device *dev) {
   cudaStreamSynchronize(dev->stream);
   if (dev->scratch) cudaFree(dev->scratch);
   if (dev->d_err) cudaFree(dev->d_err);
+  if (dev->d_work) cudaFree(dev->d_work);
   if (dev->tc_scratch) cudaFree(dev->tc_scratch);
   cudaStreamDestroy(dev->stream);
   delete dev;
@@ -453,9 +457,24 @@ static int32_t launch_gemv_nk_t(wgpt_device *dev, const float *x, size_t ldx, co
   return WGPT_OK;
 }
 
+// Matrices larger than L2 (the de-embedding): resident CTAs that loop over the columns (gemv_loop_kernel).
+template <int M>
+static int32_t launch_gemv_loop_t(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
+                                  const float *Wt, int K, int N, const Epilogue &epi, const GreedyPick &gp) {
+  constexpr int CPW = M <= 4 ? 4 : 2;
+  size_t smem = (size_t)M * K * 4;
+  auto kern = gemv_loop_kernel<M, CPW>;
+  if (smem > 48 * 1024) CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LAUNCH_PDL(dev, kern, 2 * dev->sm_count, 256, smem, x, ldx, gamma, beta, Wt, K, N, epi, gp, dev->d_work);
+  return WGPT_OK;
+}
+
 template <int M>
 static int32_t launch_gemv_nk_m(wgpt_device *dev, const float *x, size_t ldx, const float *gamma, const float *beta,
                                 const float *Wt, int K, int N, const Epilogue &epi, const GreedyPick &gp) {
+  if (dev->loop_gemv && (size_t)N * K * 4 >= (size_t(64) << 20) && N >= 64 * dev->sm_count &&
+      (size_t)M * K * 4 <= 96 * 1024)
+    return launch_gemv_loop_t<M>(dev, x, ldx, gamma, beta, Wt, K, N, epi, gp);
   // Enough warps to cover the machine several times over: split K across the warps of a CTA when N is small.
   int wk = 1;
   while (wk < 8 && (long long)N * wk < 3000 && K / (wk * 2) >= 256) wk *= 2;
@@ -1250,7 +1269,6 @@ struct wgpt_model {
   std::vector<char> have;  // per tensor slot
   bool finalized;
   std::vector<void *> allocs;
-  LayerPtrs *d_layers;  // device copy of the per-layer weight pointers (decode_persistent_kernel)
   FusedPlan fused;
 };
 
@@ -1280,7 +1298,6 @@ WGPT_EXPORT int32_t wgpt_model_create(wgpt_device *dev, const wgpt_params *param
   m->hs = hs;
   m->scale = (float)(1.0 / std::sqrt((double)hs));  // model.js:321, stored as f32 at instructions.js:1038
   m->finalized = false;
-  m->d_layers = nullptr;
   m->layers.resize(p.n_layer);
   m->have.assign(4 + 12 * (size_t)p.n_layer, 0);
   size_t E = p.n_embd, F = 4 * E;
@@ -1424,7 +1441,7 @@ template <int HS, int CS>
 static size_t attn_block_smem_t(int E, int red) { return attn_block_smem_floats<HS, CS>(E, red) * 4; }
 
 static size_t attn_block_smem(int hs, int cs, int E, int red) {
-  // 3*(hs/cs)*E + E + red + 3hs + cs*(hs+4) + hs + 8 floats (attn_block_smem_floats)
+  // attn_block_smem_floats for run-time hs, cs
   return ((size_t)3 * (hs / cs) * E + (size_t)E + red + 3 * hs + (size_t)cs * (hs + 4) + hs + 8) * 4;
 }
 
@@ -1521,11 +1538,6 @@ WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
   REQUIRE(m != nullptr, WGPT_ERR_ARG, "model handle is null");
   for (size_t i = 0; i < m->have.size(); i++)
     REQUIRE(m->have[i], WGPT_ERR_STATE, "tensor slot %zu was never set (4 + 12*layer + index)", i);
-  std::vector<LayerPtrs> lp(m->layers.size());
-  for (size_t i = 0; i < lp.size(); i++) {
-    const LayerWeights &L = m->layers[i];
-    lp[i] = LayerPtrs{L.ln1_g, L.ln1_b, L.wqkv_t, L.bqkv, L.wo_t, L.bo, L.ln2_g, L.ln2_b, L.wfc_t, L.bfc, L.wpr_t, L.bpr};
-  }
   TRY(use(m->dev));
   {
     const size_t E = m->p.n_embd, F = 4 * E;
@@ -1554,9 +1566,6 @@ WGPT_EXPORT int32_t wgpt_model_finalize(wgpt_model *m) {
       LAUNCH(m->dev, transpose_kernel, tg, dim3(32, 8), 0, (const float *)L.wpr_t, L.wpr_kn, E, F);
     }
   }
-  CK(cudaMalloc(reinterpret_cast<void **>(&m->d_layers), lp.size() * sizeof(LayerPtrs)));
-  m->allocs.push_back(m->d_layers);
-  CK(cudaMemcpyAsync(m->d_layers, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice, m->dev->stream));
   CK(cudaStreamSynchronize(m->dev->stream));
   m->finalized = true;
   return WGPT_OK;
@@ -1584,15 +1593,6 @@ struct wgpt_session {
   std::vector<uint32_t> prompts;  // host copy, [n_seq][n_prompt]
   int n_prompt, n_generated;
   bool ids_dirty;  // s->ids no longer holds the prompt window
-  // decode_persistent_kernel state
-  bool pk_ready, pk_ok;
-  DecodeParams pk;
-  size_t pk_smem;
-  unsigned long long pk_base;
-  float *pk_cand_val;
-  int *pk_cand_idx;
-  unsigned long long *pk_counter;
-  int *pk_abort;
   // top-k sampling (0 = greedy pick): parameters and the per-(step, sequence) uniform numbers on the device
   int sample_k = 0;
   double sample_temp = 1.0;
@@ -1683,7 +1683,6 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   cudaStreamSynchronize(s->m->dev->stream);
   drop_step_graph(s);
   session_free_act(s);
-  cudaFree(s->pk_cand_val); cudaFree(s->pk_cand_idx); cudaFree(s->pk_counter); cudaFree(s->pk_abort);
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
   cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
   cudaFree(s->d_uniform);
@@ -1696,11 +1695,6 @@ WGPT_EXPORT int32_t wgpt_session_reset(wgpt_session *s) {
   REQUIRE(s != nullptr, WGPT_ERR_ARG, "session handle is null");
   TRY(use(s->m->dev));
   CK(cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), s->m->dev->stream));
-  if (s->pk_counter) {  // fresh barrier numbering for the whole-token decode kernel (also clears an abandoned run)
-    CK(cudaMemsetAsync(s->pk_counter, 0, sizeof(unsigned long long), s->m->dev->stream));
-    CK(cudaMemsetAsync(s->pk_abort, 0, sizeof(int), s->m->dev->stream));
-    s->pk_base = 0;
-  }
   s->len = 0;
   return WGPT_OK;
 }
@@ -1963,96 +1957,6 @@ static int32_t pick_and_advance(wgpt_session *s, int n_tok) {
   return WGPT_OK;
 }
 
-static int pk_pick_wk(int cols, int K) {
-  int w = 1;
-  while (cols * w < 32 && w < 16 && (K / 4) / (w * 2) >= 32 && cols * w * 2 <= 1024) w *= 2;
-  return w;
-}
-
-template <int HS>
-static int32_t pk_launch_t(wgpt_session *s, cudaStream_t stream, int grid) {
-  auto kern = decode_persistent_kernel<HS>;
-  CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s->pk_smem));
-  int per_sm = 0;
-  CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kDecodeThreads, s->pk_smem));
-  REQUIRE(per_sm >= 1, WGPT_ERR_UNSUPPORTED, "the whole-token decode kernel does not fit on an SM");
-  void *args[] = {&s->pk};
-  CK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kDecodeThreads), args, s->pk_smem,
-                                 stream));
-  return WGPT_OK;
-}
-
-// Builds (once) the plan of the whole-token decode kernel for this session; pk_ok says whether it applies.
-static int32_t pk_prepare(wgpt_session *s) {
-  if (s->pk_ready) return WGPT_OK;
-  s->pk_ready = true;
-  s->pk_ok = false;
-  wgpt_model *m = s->m;
-  wgpt_device *dev = m->dev;
-  const wgpt_params &p = m->p;
-  const int E = p.n_embd, F = 4 * E, grid = dev->sm_count;
-  if (!dev->persistent || s->n_seq != 1 || E % 4 != 0) return WGPT_OK;
-  DecodeParams &k = s->pk;
-  memset(&k, 0, sizeof k);
-  k.cols_qkv = (3 * E + grid - 1) / grid; k.cols_proj = (E + grid - 1) / grid;
-  k.cols_fc = (F + grid - 1) / grid; k.cols_down = (E + grid - 1) / grid;
-  k.wk_qkv = pk_pick_wk(k.cols_qkv, E); k.wk_proj = pk_pick_wk(k.cols_proj, E);
-  k.wk_fc = pk_pick_wk(k.cols_fc, E); k.wk_down = pk_pick_wk(k.cols_down, F);
-  size_t wb = (size_t)k.cols_qkv * E;
-  if ((size_t)k.cols_fc * E > wb) wb = (size_t)k.cols_fc * E;
-  if ((size_t)k.cols_down * F > wb) wb = (size_t)k.cols_down * F;
-  wb = (wb + 31) & ~size_t(31);
-  k.wbuf_floats = (int)wb;
-  s->pk_smem = (2 * wb + 4 * (size_t)E + E + 1024) * 4 + 64;
-  if (s->pk_smem + 8192 > dev->smem_optin) return WGPT_OK;  // e.g. GPT-2 XL: blocks too large, keep the kernel chain
-  if (k.cols_qkv * k.wk_qkv > 1024 || k.cols_fc * k.wk_fc > 1024) return WGPT_OK;
-  CK(cudaMalloc(&s->pk_cand_val, grid * sizeof(float)));
-  CK(cudaMalloc(&s->pk_cand_idx, grid * sizeof(int)));
-  CK(cudaMalloc(&s->pk_counter, sizeof(unsigned long long)));
-  CK(cudaMalloc(&s->pk_abort, sizeof(int)));
-  CK(cudaMemsetAsync(s->pk_counter, 0, sizeof(unsigned long long), dev->stream));
-  CK(cudaMemsetAsync(s->pk_abort, 0, sizeof(int), dev->stream));
-  s->pk_base = 0;
-  k.layers = m->d_layers;
-  k.n_layer = p.n_layer; k.E = E; k.H = p.n_head; k.n_ctx = p.n_ctx; k.V = p.vocab_size;
-  k.wte = m->wte; k.wpe = m->wpe; k.lnf_g = m->lnf_g; k.lnf_b = m->lnf_b;
-  k.kc = s->kc; k.vc = s->vc; k.kv_layer_stride = (size_t)s->n_seq * p.n_ctx * E;
-  k.attn_part = s->attn_part; k.cand_val = s->pk_cand_val; k.cand_idx = s->pk_cand_idx;
-  k.next_id = s->next_ids; k.pos = s->d_pos; k.step = s->d_step;
-  k.bar_counter = s->pk_counter; k.err = dev->d_err; k.abort_word = s->pk_abort;
-  k.scale = m->scale; k.rows_deembed = (p.vocab_size + grid - 1) / grid; k.nsl = s->n_split;
-  s->pk_ok = true;
-  return WGPT_OK;
-}
-
-// n_steps greedy decode steps of a single sequence in one cooperative launch.
-static int32_t decode_steps_persistent(wgpt_session *s, int n_steps) {
-  wgpt_device *dev = s->m->dev;
-  DecodeParams &k = s->pk;
-  TRY(session_reserve(s, 1));
-  k.x = s->x; k.q = s->q; k.f = s->f; k.logits = s->logits;   // activation buffers may have been re-allocated
-  k.out_ids = s->out_ids;
-  k.n_steps = n_steps;
-  k.bar_base = s->pk_base;
-  const int grid = dev->sm_count;
-  int32_t rc = WGPT_OK;
-  switch (s->m->hs) {
-    case 4: rc = pk_launch_t<4>(s, dev->stream, grid); break;
-    case 8: rc = pk_launch_t<8>(s, dev->stream, grid); break;
-    case 16: rc = pk_launch_t<16>(s, dev->stream, grid); break;
-    case 32: rc = pk_launch_t<32>(s, dev->stream, grid); break;
-    case 64: rc = pk_launch_t<64>(s, dev->stream, grid); break;
-    case 128: rc = pk_launch_t<128>(s, dev->stream, grid); break;
-    default: return fail(WGPT_ERR_UNSUPPORTED, "head_size %d", s->m->hs);
-  }
-  TRY(rc);
-  dev->launches++;
-  s->pk_base += (unsigned long long)n_steps * (5ULL * s->m->p.n_layer + 2ULL) * (unsigned long long)grid;
-  s->len += n_steps;
-  s->last_rows = 1;
-  return WGPT_OK;
-}
-
 // One decode step (newest token of every sequence -> next token), replayed as a CUDA graph: all position- and
 // step-dependent values are read from device memory, so one captured step serves every position.
 static int32_t decode_step(wgpt_session *s) {
@@ -2187,17 +2091,7 @@ static int32_t generate(wgpt_session *s, int32_t n_new) {
     s->ids_dirty = false;
   }
   TRY(forward(s, s->ids, first, true));
-  TRY(pk_prepare(s));
-  int i_start = 1;
-  if (s->pk_ok && n_new > 1 && s->sample_k == 0) {
-    // all remaining steps that fit in the context window run inside one persistent kernel
-    int fit = n_ctx - s->len;
-    int run = n_new - 1 < fit ? n_new - 1 : fit;
-    if (run > 0) {
-      TRY(decode_steps_persistent(s, run));
-      i_start += run;
-    }
-  }
+  const int i_start = 1;
   for (int i = i_start; i < n_new; i++) {
     if (s->len + 1 <= n_ctx) {
       TRY(decode_step(s));

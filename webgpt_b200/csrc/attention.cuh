@@ -49,8 +49,12 @@ attn_decode_kernel(const float *__restrict__ q, int ldq, const float *__restrict
     const int Ls = __ldcg(pos) + 1;
     const int chunk_s = (Ls + n_split - 1) / n_split;
     const int beg_s = split * chunk_s, end_s = min(Ls, beg_s + chunk_s);
-    for (int r = beg_s + (tid >> 1); r < end_s; r += 128)
-      prefetch_l2(((tid & 1) ? vb : kb) + (size_t)r * ldkv, HS * 4);
+    constexpr int LPR = HS * 4 >= 128 ? HS * 4 / 128 : 1;  // 128-byte lines per row slice
+    const int total = max(end_s - beg_s, 0) * 2 * LPR;
+    for (int i = tid; i < total; i += 256) {
+      const int r = beg_s + i / (2 * LPR), w = i % (2 * LPR);
+      prefetch_line_l2((w < LPR ? kb : vb) + (size_t)r * ldkv + (w % LPR) * 32);
+    }
   }
   pdl_wait();  // q, the cache row of this step and *pos come from earlier kernels
   trace(3, 1);

@@ -141,6 +141,12 @@ __device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
+// Asks for the 128-byte line that holds p in L2 through the load/store unit. Used where many small strided pieces
+// are wanted (rows of the K/V cache): hundreds of bulk prefetch requests from one CTA, issued while another CTA of
+// the same SM had bulk copies in flight, coincided with launch failures, so the bulk-copy engine is kept for few,
+// large requests.
+__device__ __forceinline__ void prefetch_line_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // ---- bulk asynchronous copy (TMA, untiled form) global -> shared, completion counted on an mbarrier ----
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -193,5 +199,34 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 __device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+
+// LayerNorm of one row of E floats (normStats + norm, instructions.js:451-550) by a whole CTA of NT threads:
+// thread t < E/4 holds elements 4t..4t+3 in v. Two block-wide sums (mean, then the squared deviations from it),
+// each a warp butterfly plus a fixed-order sum of the warps' results; sred needs 2*NT/32 floats. Returns the
+// normalised elements; multiplies by 1/sd where the shader divides (at most one unit in the last place apart).
+template <int NT>
+__device__ __forceinline__ float4 block_layernorm4(float4 v, bool has, int E, float4 g, float4 b, float *sred) {
+  constexpr int NW = NT / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float s = has ? (v.x + v.y) + (v.z + v.w) : 0.f;
+  s = warp_sum(s);
+  if (lane == 0) sred[warp] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; w++) tot += sred[w];
+  const float mean = tot / (float)E;
+  const float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
+  float q = has ? (dx * dx + dy * dy) + (dz * dz + dw * dw) : 0.f;
+  q = warp_sum(q);
+  if (lane == 0) sred[NW + warp] = q;
+  __syncthreads();
+  float qt = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; w++) qt += sred[NW + w];
+  const float rsd = 1.0f / sqrtf(qt / (float)E + 1e-5f);
+  return make_float4(g.x * (dx * rsd) + b.x, g.y * (dy * rsd) + b.y, g.z * (dz * rsd) + b.z, g.w * (dw * rsd) + b.w);
+}
+
 
 }  // namespace wgpt

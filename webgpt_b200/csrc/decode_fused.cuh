@@ -120,34 +120,6 @@ __device__ __forceinline__ float4 halfwarp_rows_sum(const float4 *__restrict__ b
 constexpr int kAttnSumRows = 10;  // attn_block_kernel / finish_row_kernel: partial rows <= 10 * 8 warps
 constexpr int kMlpSumRows = 8;    // mlp_block_kernel: partial rows (heads) <= 2 * 8
 
-// LayerNorm of one row of E floats (normStats + norm, instructions.js:451-550) by a whole CTA of NT threads:
-// thread t < E/4 holds elements 4t..4t+3 in v. Two block-wide sums (mean, then the squared deviations from it),
-// each a warp butterfly plus a fixed-order sum of the warps' results; sred needs 2*NT/32 floats. Returns the
-// normalised elements; multiplies by 1/sd where the shader divides (at most one unit in the last place apart).
-template <int NT>
-__device__ __forceinline__ float4 block_layernorm4(float4 v, bool has, int E, float4 g, float4 b, float *sred) {
-  constexpr int NW = NT / 32;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float s = has ? (v.x + v.y) + (v.z + v.w) : 0.f;
-  s = warp_sum(s);
-  if (lane == 0) sred[warp] = s;
-  __syncthreads();
-  float tot = 0.f;
-#pragma unroll
-  for (int w = 0; w < NW; w++) tot += sred[w];
-  const float mean = tot / (float)E;
-  const float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
-  float q = has ? (dx * dx + dy * dy) + (dz * dz + dw * dw) : 0.f;
-  q = warp_sum(q);
-  if (lane == 0) sred[NW + warp] = q;
-  __syncthreads();
-  float qt = 0.f;
-#pragma unroll
-  for (int w = 0; w < NW; w++) qt += sred[NW + w];
-  const float rsd = 1.0f / sqrtf(qt / (float)E + 1e-5f);
-  return make_float4(g.x * (dx * rsd) + b.x, g.y * (dy * rsd) + b.y, g.z * (dz * rsd) + b.z, g.w * (dw * rsd) + b.w);
-}
-
 // Asks for a contiguous block in L2, in pieces of at most 16 KB.
 __device__ __forceinline__ void prefetch_l2_block(const void *src, uint32_t bytes) {
   for (uint32_t off = 0; off < bytes; off += 16384u)
@@ -273,8 +245,12 @@ attn_block_kernel(AttnBlockParams p) {
     const int Ls = __ldcg(p.pos) + 1;
     const int chunk_s = (Ls + CS - 1) / CS;
     const int beg_s = (int)rank * chunk_s, end_s = min(Ls, beg_s + chunk_s);
-    for (int r = beg_s + (tid >> 1); r < end_s; r += NT / 2)
-      prefetch_l2(((tid & 1) ? vb : kb) + (size_t)r * E, HS * 4);
+    constexpr int LPR = HS * 4 >= 128 ? HS * 4 / 128 : 1;  // 128-byte lines per row slice
+    const int total = max(end_s - beg_s, 0) * 2 * LPR;
+    for (int i = tid; i < total; i += NT) {
+      const int r = beg_s + i / (2 * LPR), w = i % (2 * LPR);
+      prefetch_line_l2((w < LPR ? kb : vb) + (size_t)r * E + (w % LPR) * 32);
+    }
   }
   cluster_arrive();  // pairs with the wait below: every CTA of the cluster is running before any remote store
   if (tid == 0) {  // the q/k/v weights into shared memory, the projection slice towards L2
@@ -285,6 +261,10 @@ attn_block_kernel(AttnBlockParams p) {
   const int pos = __ldcg(p.pos);
   trace(8, 1);
 
+  // Global stores are held back until after the last cluster barrier: a releasing barrier arrival waits for the
+  // acknowledgement of every store issued before it, and with the next kernel's weight burst in flight towards the
+  // same SM such an acknowledgement took about 3 us.
+  float4 x_keep = make_float4(0.f, 0.f, 0.f, 0.f);
   // ---- the residual stream: this CTA sums columns [col0, col0 + ncolA) and hands them to the whole cluster.
   //      One group of 16 lanes per float4 column; lane 0 of the group adds the row the partial results belong to.
   {
@@ -310,7 +290,6 @@ attn_block_kernel(AttnBlockParams p) {
     // Only now may the next kernel start. Its CTAs fetch 19 MB of weights the moment they start, and while such a
     // burst is in flight this kernel's small latency-critical loads (the partial results above) wait behind it:
     // measured 4.7 us for the loads above with the next kernel already fetching, 1.3 us without.
-    pdl_launch_dependents();
     cluster_wait();
     if (tid < ncol4) {
       float4 x = x0;
@@ -318,7 +297,7 @@ attn_block_kernel(AttnBlockParams p) {
       for (int w = 0; w < NW; w++) x = add4(x, reinterpret_cast<const float4 *>(red)[w * 32 + tid]);
 #pragma unroll
       for (int cc = 0; cc < CS; cc++) dsmem_st4(dsmem_addr(xs + col0 + 4 * tid, (uint32_t)cc), x);
-      if (h == 0) reinterpret_cast<float4 *>(p.x_out + col0)[tid] = x;
+      x_keep = x;
     }
   }
   trace(8, 2);
@@ -345,6 +324,7 @@ attn_block_kernel(AttnBlockParams p) {
       mbar_wait(&bars[0], 0, kFusedPolls << 2);
     }
   }
+  float kv_keep[NB];  // the new k and v values, written to the cache at the end of the kernel
   {
     const float4 *w4 = reinterpret_cast<const float4 *>(wbuf);
     const float4 *h4 = reinterpret_cast<const float4 *>(hn);
@@ -365,17 +345,16 @@ attn_block_kernel(AttnBlockParams p) {
     for (int b = 0; b < NB; b++) {
       const int c = warp + NW * b;
       const float v = warp_sum(acc[b]) + bias_c[b];
+      kv_keep[b] = v;
       if (c < NC) {
         const int sec = c / NQ, d = (int)rank * NQ + (c % NQ);
         float *dst = sec == 0 ? qfull : (sec == 1 ? knew : vnew);
         if (lane < CS) dsmem_st(dsmem_addr(dst + d, (uint32_t)lane), v);
-        // the new rows also go to the cache for later steps (this step reads them from shared memory)
-        if (lane == CS && sec == 1) p.kc[(size_t)pos * E + h * HS + d] = v;
-        if (lane == CS && sec == 2) p.vc[(size_t)pos * E + h * HS + d] = v;
       }
     }
   }
   __syncthreads();  // every warp is done with the q/k/v weights
+  trace(8, 11);
   cluster_arrive();
   if (tid == 0) {   // fetch the projection slice into their place while the cluster barrier completes
     fence_proxy_async();
@@ -465,6 +444,7 @@ attn_block_kernel(AttnBlockParams p) {
     }
   }
   trace(8, 7);
+  pdl_launch_dependents();
   cluster_arrive();
   cluster_wait();
   trace(8, 8);
@@ -505,6 +485,19 @@ attn_block_kernel(AttnBlockParams p) {
       float s = red[tid];
       for (int q = 1; q < p.proj_parts; q++) s += red[q * ncolA + tid];
       p.part_out[(size_t)h * E + col0 + tid] = s;
+    }
+  }
+  // ---- the held-back stores: the residual stream for the MLP kernel, and the new k, v rows for later steps (this
+  //      step read them from shared memory)
+  if (h == 0 && tid < ncol4) reinterpret_cast<float4 *>(p.x_out + col0)[tid] = x_keep;
+  if (lane == 0) {
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const int c = warp + NW * b;
+      if (c < NC && c >= NQ) {
+        const int sec = c / NQ, d = (int)rank * NQ + (c % NQ);
+        (sec == 1 ? p.kc : p.vc)[(size_t)pos * E + h * HS + d] = kv_keep[b];
+      }
     }
   }
   trace(8, 10);
@@ -586,6 +579,8 @@ mlp_block_kernel(MlpBlockParams p) {
   trace(9, 1);
 
   // ---- residual stream: xin + bias + the per-head partial results for this CTA's share of the columns
+  float4 x_keep = make_float4(0.f, 0.f, 0.f, 0.f);
+  int x_col = -1;
   {
     const int cbase = (int)rank * nq4;
     const int c = warp * 16 + (lane & 15);  // one warp per 16 columns, its two halves take alternate rows
@@ -593,6 +588,7 @@ mlp_block_kernel(MlpBlockParams p) {
     const float4 sum = halfwarp_rows_sum<kMlpSumRows>(reinterpret_cast<const float4 *>(p.part_in) + cbase + warp * 16,
                                                      min(16, max(nq4 - warp * 16, 0)), (size_t)E4, p.n_part, lane);
     float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    x_col = cbase + c;
     if (mine)
       x0 = add4(__ldcg(reinterpret_cast<const float4 *>(p.xin) + cbase + c),
                 reinterpret_cast<const float4 *>(p.bias_in)[cbase + c]);
@@ -601,13 +597,14 @@ mlp_block_kernel(MlpBlockParams p) {
       const float4 x = add4(x0, sum);
 #pragma unroll
       for (int cc = 0; cc < CS; cc++) dsmem_st4(dsmem_addr(xs + 4 * (cbase + c), (uint32_t)cc), x);
-      if (blockIdx.x < CS) reinterpret_cast<float4 *>(p.x_out)[cbase + c] = x;
+      if (blockIdx.x < CS) x_keep = x;  // stored after the last cluster barrier (see attn_block_kernel)
+      else x_col = -1;
+    } else {
+      x_col = -1;
     }
   }
   cluster_arrive();
   cluster_wait();
-  // Only now may the next kernel start fetching its weights (see attn_block_kernel).
-  pdl_launch_dependents();
   trace(9, 2);
   {
     const bool has = tid < E4;
@@ -660,6 +657,8 @@ mlp_block_kernel(MlpBlockParams p) {
     for (int k = 0; k < p.wk; k++) v += red[tid * p.wk + k];
     gs[tid] = gelu_f(v + bias_u);
   }
+  // Only now may the next kernel start fetching its weights (see attn_block_kernel).
+  pdl_launch_dependents();
   trace(9, 5);
   {
     const int landed = __syncthreads_and(mbar_wait(&bars[1], 0, kFusedPolls) ? 1 : 0);
@@ -701,6 +700,7 @@ mlp_block_kernel(MlpBlockParams p) {
     for (int r = 1; r < CS; r++) a = add4(a, x4[r * nq4 + tid]);
     reinterpret_cast<float4 *>(p.part_out + (size_t)(blockIdx.x / CS) * E)[(int)rank * nq4 + tid] = a;
   }
+  if (x_col >= 0) reinterpret_cast<float4 *>(p.x_out)[x_col] = x_keep;
   trace(9, 7);
 }
 

@@ -29,6 +29,58 @@ struct GreedyPick {
   int n_tok;
 };
 
+// Second half of the greedy pick: thread m < M of every CTA brings the CTA's best (value, index) of row m; the
+// last CTA to arrive reduces the candidates of all CTAs (lowest index wins ties), writes the next input id and the
+// output list entry, and advances the position and step counters. All 256 threads of the CTA must call it.
+template <int M>
+__device__ __forceinline__ void greedy_pick_finish(const GreedyPick &gp, float bv, int bn) {
+  __shared__ float fin_v[8];
+  __shared__ int fin_n[8];
+  __shared__ unsigned int is_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < M) {
+    gp.pval[(size_t)tid * gridDim.x + blockIdx.x] = bv;
+    gp.pidx[(size_t)tid * gridDim.x + blockIdx.x] = bn;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = (atomicAdd(gp.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int my_step = __ldcg(gp.step);
+  for (int m = 0; m < M; m++) {
+    bv = -INFINITY;
+    bn = 0x7fffffff;
+    for (int j = tid; j < (int)gridDim.x; j += 256) {
+      float v = __ldcg(gp.pval + (size_t)m * gridDim.x + j);
+      int n = __ldcg(gp.pidx + (size_t)m * gridDim.x + j);
+      if (v > bv || (v == bv && n < bn)) { bv = v; bn = n; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int on = __shfl_xor_sync(0xffffffffu, bn, o);
+      if (ov > bv || (ov == bv && on < bn)) { bv = ov; bn = on; }
+    }
+    __syncthreads();  // fin_* are re-used from one row to the next
+    if (lane == 0) { fin_v[warp] = bv; fin_n[warp] = bn; }
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < 8; w++)
+        if (fin_v[w] > bv || (fin_v[w] == bv && fin_n[w] < bn)) { bv = fin_v[w]; bn = fin_n[w]; }
+      if (bn == 0x7fffffff) bn = 0;  // a row of NaNs compares false everywhere: report index 0
+      gp.next_ids[m] = (uint32_t)bn;
+      if (gp.out_ids) gp.out_ids[(size_t)m * gp.out_stride + my_step] = (uint32_t)bn;
+    }
+  }
+  if (tid == 0) {
+    *gp.pos = __ldcg(gp.pos) + gp.n_tok;
+    *gp.step = my_step + 1;
+    *gp.counter = 0u;
+  }
+}
+
 // x: [M, K] rows at stride ldx; Wt: [N, K]. CTA = 8 warps = (8/WK) column groups x WK slices of K.
 // Each warp accumulates CPW columns over its K slice for all M rows.
 // Order of work: (1) allow the next kernel to launch and put this warp's first weights in flight (weights are
@@ -176,60 +228,214 @@ gemv_nk_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict_
   if (gp.pval == nullptr) return;
 
   // ---- greedy pick ----
-  constexpr int NC = WC * CPW * M < 8 ? 8 : WC * CPW * M;  // also holds one candidate per warp in the final reduction
+  constexpr int NC = WC * CPW * M;
   __shared__ float cand_v[NC];
   __shared__ int cand_n[NC];
-  __shared__ unsigned int is_last;
-  if (tid < WC * CPW * M) { cand_v[tid] = outv; cand_n[tid] = outn; }
+  if (tid < NC) { cand_v[tid] = outv; cand_n[tid] = outn; }
   __syncthreads();
+  float bv = -INFINITY;
+  int bn = 0x7fffffff;
   if (tid < M) {  // candidates of row m sit at tid + M*j; columns ascend with j, so ">" keeps the lowest index
-    float bv = -INFINITY;
-    int bn = 0x7fffffff;
     for (int j = 0; j < WC * CPW; j++) {
       float v = cand_v[tid + M * j];
       int n = cand_n[tid + M * j];
       if (v > bv || (v == bv && n < bn)) { bv = v; bn = n; }
     }
-    gp.pval[(size_t)tid * gridDim.x + blockIdx.x] = bv;
-    gp.pidx[(size_t)tid * gridDim.x + blockIdx.x] = bn;
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) is_last = (atomicAdd(gp.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  const int my_step = __ldcg(gp.step);
-  for (int m = 0; m < M; m++) {
-    float bv = -INFINITY;
-    int bn = 0x7fffffff;
-    for (int j = tid; j < (int)gridDim.x; j += 256) {
-      float v = __ldcg(gp.pval + (size_t)m * gridDim.x + j);
-      int n = __ldcg(gp.pidx + (size_t)m * gridDim.x + j);
-      if (v > bv || (v == bv && n < bn)) { bv = v; bn = n; }
-    }
+  greedy_pick_finish<M>(gp, bv, bn);
+}
+
+// ------------------------------------------------------------------------------------------------
+// gemv_loop_kernel: the product of gemv_nk_kernel for a matrix larger than L2 (the tied de-embedding,
+// model.js:224-229: 50257 x n_embd floats per token). A few CTAs per SM stay resident and every warp walks a
+// contiguous range of columns, CPW at a time, so the input rows are staged and normalised once per CTA instead of
+// once per 32 columns, and the warps never meet at a barrier inside the loop: their loads stay spread over time and
+// the stream has no per-CTA start and tail. Optional greedy pick as in gemv_nk_kernel.
+// Dynamic shared memory: M*K floats. HBM-bound: bytes = 4*N*K per launch.
+template <int M, int CPW>
+__global__ void __maxnreg__(96)
+gemv_loop_kernel(const float *__restrict__ x, size_t ldx, const float *__restrict__ gamma,
+                 const float *__restrict__ beta, const float *__restrict__ Wt, int K, int N, Epilogue epi,
+                 GreedyPick gp, unsigned int *__restrict__ work) {
+  extern __shared__ __align__(128) float smem[];
+  float *xs = smem;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K4 = K >> 2;
+  // Work is handed out CPW columns at a time: the first chunk of every warp is fixed (so its first loads can be
+  // issued ahead of the dependency wait), the rest comes from a counter, because SMs do not all get the same share
+  // of the memory bandwidth and equal shares of the columns left the slowest ones 6 us behind. work[0] counts the
+  // chunks handed out beyond the fixed ones, work[1] the CTAs that are done; the last CTA leaves both zero.
+  const int gw = blockIdx.x * 8 + warp, tw = gridDim.x * 8;
+  const int c_beg = gw * CPW;
+  TRACE_BEGIN(5);
+  trace(5, 0);
+  // first loads of this warp's first columns: weights are written by no kernel, so they may be requested while the
+  // previous kernel is still running
+  constexpr int PRE = 2;
+  float4 wpre[CPW][PRE];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      int on = __shfl_xor_sync(0xffffffffu, bn, o);
-      if (ov > bv || (ov == bv && on < bn)) { bv = ov; bn = on; }
+  for (int c = 0; c < CPW; c++) {
+    const int col = min(c_beg + c, N - 1);
+#pragma unroll
+    for (int j = 0; j < PRE; j++) {
+      const int i = lane + 32 * j;
+      wpre[c][j] = i < K4 ? ldg_stream4(reinterpret_cast<const float4 *>(Wt + (size_t)col * K) + i)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    __syncthreads();  // cand_* reuse
-    if (lane == 0) { cand_v[warp] = bv; cand_n[warp] = bn; }
+  }
+  // gamma and beta are weights too
+  const bool one_pass = M == 1 && K4 <= 256;  // the whole row fits one float4 per thread: block-wide LayerNorm
+  float4 g_first = make_float4(1.f, 1.f, 1.f, 1.f), b_first = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (one_pass && gamma != nullptr && tid < K4) {
+    g_first = reinterpret_cast<const float4 *>(gamma)[tid];
+    b_first = reinterpret_cast<const float4 *>(beta)[tid];
+  }
+  pdl_wait();
+  trace(5, 1);
+  if (one_pass) {
+    __shared__ float ln_red[16];
+    const bool has = tid < K4;
+    float4 v = has ? __ldcg(reinterpret_cast<const float4 *>(x) + tid) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gamma != nullptr) v = block_layernorm4<256>(v, has, K, g_first, b_first, ln_red);
+    if (has) reinterpret_cast<float4 *>(xs)[tid] = v;
     __syncthreads();
-    if (tid == 0) {
-      for (int w = 1; w < 8; w++)
-        if (cand_v[w] > bv || (cand_v[w] == bv && cand_n[w] < bn)) { bv = cand_v[w]; bn = cand_n[w]; }
-      if (bn == 0x7fffffff) bn = 0;  // a row of NaNs compares false everywhere: report index 0
-      gp.next_ids[m] = (uint32_t)bn;
-      if (gp.out_ids) gp.out_ids[(size_t)m * gp.out_stride + my_step] = (uint32_t)bn;
+    pdl_launch_dependents();
+  } else {
+    {
+      float4 *xs4w = reinterpret_cast<float4 *>(xs);
+      const size_t ldx4 = ldx >> 2;
+      const float4 *x4 = reinterpret_cast<const float4 *>(x);
+      for (int idx = tid; idx < M * K4; idx += 256) {
+        int m = idx / K4, i = idx - m * K4;
+        xs4w[idx] = __ldcg(x4 + (size_t)m * ldx4 + i);
+      }
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    if (gamma != nullptr) {  // LayerNorm (instructions.js:451-550), one warp per row, two passes over the row
+      for (int m = warp; m < M; m += 8) {
+        float4 *row = reinterpret_cast<float4 *>(xs + (size_t)m * K);
+        float s = 0.f;
+        for (int i = lane; i < K4; i += 32) {
+          float4 v = row[i];
+          s += (v.x + v.y) + (v.z + v.w);
+        }
+        float mean = warp_sum(s) / (float)K;
+        float q = 0.f;
+        for (int i = lane; i < K4; i += 32) {
+          float4 v = row[i];
+          float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+          q += (a * a + b * b) + (c * c + d * d);
+        }
+        float sd = sqrtf(warp_sum(q) / (float)K + 1e-5f);
+        const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
+        const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+        for (int i = lane; i < K4; i += 32) {
+          float4 v = row[i], g = g4[i], b = b4[i];
+          row[i] = make_float4(g.x * ((v.x - mean) / sd) + b.x, g.y * ((v.y - mean) / sd) + b.y,
+                               g.z * ((v.z - mean) / sd) + b.z, g.w * ((v.w - mean) / sd) + b.w);
+        }
+      }
+      __syncthreads();
     }
   }
-  if (tid == 0) {
-    *gp.pos = __ldcg(gp.pos) + gp.n_tok;
-    *gp.step = my_step + 1;
-    *gp.counter = 0u;
+  trace(5, 2);
+
+  const float4 *xs4 = reinterpret_cast<const float4 *>(xs);
+  float bv[M];
+  int bn[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) { bv[m] = -INFINITY; bn[m] = 0x7fffffff; }
+  unsigned int grabbed = 0;  // lane 0: the request for the chunk after the current one, issued one chunk ahead
+  if (lane == 0) grabbed = atomicAdd(&work[0], 1u);
+  int c0 = c_beg;
+  while (c0 < N) {
+    const int c_end = min(c0 + CPW, N);
+    const float4 *w4[CPW];
+#pragma unroll
+    for (int c = 0; c < CPW; c++) w4[c] = reinterpret_cast<const float4 *>(Wt + (size_t)min(c0 + c, N - 1) * K);
+    float acc[CPW][M];
+#pragma unroll
+    for (int c = 0; c < CPW; c++)
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[c][m] = 0.f;
+    int i0 = lane;
+    if (c0 == c_beg) {  // the loads issued ahead of the dependency wait
+#pragma unroll
+      for (int j = 0; j < PRE; j++) {
+        const int i = lane + 32 * j;
+        if (i < K4) {
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            const float4 xv = xs4[(size_t)m * K4 + i];
+#pragma unroll
+            for (int c = 0; c < CPW; c++) acc[c][m] += dot4(wpre[c][j], xv);
+          }
+        }
+      }
+      i0 = lane + 32 * PRE;
+    }
+#pragma unroll 4
+    for (int i = i0; i < K4; i += 32) {
+      float4 w[CPW];
+#pragma unroll
+      for (int c = 0; c < CPW; c++) w[c] = ldg_stream4(w4[c] + i);
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const float4 xv = xs4[(size_t)m * K4 + i];
+#pragma unroll
+        for (int c = 0; c < CPW; c++) acc[c][m] += dot4(w[c], xv);
+      }
+    }
+    // every lane ends up with every sum; lane c*M + m stores column c0+c of row m
+    float mine = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPW; c++)
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const int n = c0 + c;
+        float v = warp_sum(acc[c][m]);
+        if (n < c_end) {  // same for the whole warp
+          v = epi_apply(epi, v, m, n);
+          if (lane == c * M + m) mine = v;
+          if (v > bv[m]) { bv[m] = v; bn[m] = n; }  // columns ascend: the lowest index of equal values is kept
+        }
+      }
+    if (lane < CPW * M) {
+      const int c = lane / M, m = lane - c * M;
+      if (c0 + c < c_end) *epi_addr(epi, m, c0 + c) = mine;
+    }
+    const long long nxt = ((long long)tw + (long long)__shfl_sync(0xffffffffu, grabbed, 0)) * CPW;
+    if (nxt >= N) break;
+    c0 = (int)nxt;
+    if (lane == 0) grabbed = atomicAdd(&work[0], 1u);
   }
+  trace(5, 3);
+  __syncthreads();  // every warp of this CTA has made its last request
+  if (tid == 0 && atomicAdd(&work[1], 1u) == gridDim.x - 1) {
+    work[0] = 0u;
+    work[1] = 0u;
+  }
+  if (gp.pval == nullptr) return;
+
+  // ---- greedy pick: the warps' candidates of each row, then the CTA's
+  __shared__ float cand_v[8 * M];
+  __shared__ int cand_n[8 * M];
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < M; m++) { cand_v[warp * M + m] = bv[m]; cand_n[warp * M + m] = bn[m]; }
+  }
+  __syncthreads();
+  float cv = -INFINITY;
+  int cn = 0x7fffffff;
+  if (tid < M) {
+    for (int w = 0; w < 8; w++) {
+      const float v = cand_v[w * M + tid];
+      const int n = cand_n[w * M + tid];
+      if (v > cv || (v == cv && n < cn)) { cv = v; cn = n; }
+    }
+  }
+  greedy_pick_finish<M>(gp, cv, cn);
 }
 
 // ------------------------------------------------------------------------------------------------
