@@ -1589,6 +1589,7 @@ struct wgpt_session {
   uint32_t *ids, *next_ids, *out_ids;
   float *pick_val;  // [n_seq][vocab] per-CTA arg-max candidates of the fused greedy pick
   int *pick_idx;
+  unsigned long long *pick_keys;  // [8] (value, index) keys of gemv_loop_kernel's greedy pick, zero between launches
   int *d_pos, *d_step;
   std::vector<uint32_t> prompts;  // host copy, [n_seq][n_prompt]
   int n_prompt, n_generated;
@@ -1653,6 +1654,8 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_val, (size_t)n_seq * p.vocab_size * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_idx, (size_t)n_seq * p.vocab_size * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->pick_keys, 8 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemsetAsync(s->pick_keys, 0, 8 * sizeof(unsigned long long), m->dev->stream);
   if (e == cudaSuccess) e = cudaMalloc(&s->d_pos, 2 * sizeof(int));
   if (e == cudaSuccess && m->fused.ok && n_seq == 1) {
     const size_t E = p.n_embd;
@@ -1665,7 +1668,7 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   if (e == cudaSuccess) e = cudaMemsetAsync(s->d_pos, 0, 2 * sizeof(int), m->dev->stream);
   if (e != cudaSuccess) {
     cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
-    cudaFree(s->next_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
+    cudaFree(s->next_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx); cudaFree(s->pick_keys);
     cudaFree(s->fx_a); cudaFree(s->fx_b); cudaFree(s->fpart_a); cudaFree(s->fpart_b);
     delete s;
     return fail(e == cudaErrorMemoryAllocation ? WGPT_ERR_OOM : WGPT_ERR_CUDA, "session allocation: %s",
@@ -1684,7 +1687,7 @@ WGPT_EXPORT int32_t wgpt_session_destroy(wgpt_session *s) {
   drop_step_graph(s);
   session_free_act(s);
   cudaFree(s->kc); cudaFree(s->vc); cudaFree(s->logits); cudaFree(s->attn_part); cudaFree(s->attn_cnt);
-  cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx);
+  cudaFree(s->next_ids); cudaFree(s->out_ids); cudaFree(s->d_pos); cudaFree(s->pick_val); cudaFree(s->pick_idx); cudaFree(s->pick_keys);
   cudaFree(s->d_uniform);
   cudaFree(s->fx_a); cudaFree(s->fx_b); cudaFree(s->fpart_a); cudaFree(s->fpart_b);
   delete s;
@@ -1863,6 +1866,11 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
       gp.pval = s->pick_val; gp.pidx = s->pick_idx; gp.counter = s->attn_cnt + (size_t)s->n_seq * H;
       gp.next_ids = s->next_ids; gp.out_ids = s->out_ids; gp.out_stride = s->out_cap;
       gp.pos = s->d_pos; gp.step = s->d_step; gp.n_tok = n_tok;
+      gp.keys = s->pick_keys;
+      if (s->n_seq == 1 && m->fused.ok && s->fx_a != nullptr) {  // the next step's first kernel finds its weights in L2
+        gp.next_w = reinterpret_cast<const char *>(m->layers[0].attn_blk);
+        gp.next_w_bytes = (unsigned int)((size_t)H * m->fused.cs * m->fused.blk_floats * 4);
+      }
     }
     TRY(launch_gemv_nk(dev, s->n_seq, x_last, ld_last, m->lnf_g, m->lnf_b, m->wte, E, p.vocab_size, e, gp));
     if (pick && s->sample_k > 0) return pick_and_advance(s, n_tok);

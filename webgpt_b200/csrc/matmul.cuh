@@ -27,6 +27,11 @@ struct GreedyPick {
   int out_stride;
   int *pos, *step;
   int n_tok;
+  // gemv_loop_kernel only: one 64-bit (value, index) key per row, zero on entry and left zero, and a weight block
+  // the kernel asks for in L2 when its own work is done (the next kernel's; may be null)
+  unsigned long long *keys;
+  const char *next_w;
+  unsigned int next_w_bytes;
 };
 
 // Second half of the greedy pick: thread m < M of every CTA brings the CTA's best (value, index) of row m; the
@@ -411,31 +416,52 @@ gemv_loop_kernel(const float *__restrict__ x, size_t ldx, const float *__restric
     if (lane == 0) grabbed = atomicAdd(&work[0], 1u);
   }
   trace(5, 3);
-  __syncthreads();  // every warp of this CTA has made its last request
-  if (tid == 0 && atomicAdd(&work[1], 1u) == gridDim.x - 1) {
-    work[0] = 0u;
-    work[1] = 0u;
-  }
-  if (gp.pval == nullptr) return;
-
-  // ---- greedy pick: the warps' candidates of each row, then the CTA's
-  __shared__ float cand_v[8 * M];
-  __shared__ int cand_n[8 * M];
-  if (lane == 0) {
+  // ---- greedy pick: every warp folds its best (value, index) of each row into one 64-bit key per row with an
+  // atomic maximum (value in sortable form in the high word, 2^32-1 - index in the low word, so the lowest index
+  // wins ties; a row of NaNs leaves the key zero and reports index 0); the last CTA to finish reads the keys.
+  if (gp.keys != nullptr && lane == 0) {
 #pragma unroll
-    for (int m = 0; m < M; m++) { cand_v[warp * M + m] = bv[m]; cand_n[warp * M + m] = bn[m]; }
-  }
-  __syncthreads();
-  float cv = -INFINITY;
-  int cn = 0x7fffffff;
-  if (tid < M) {
-    for (int w = 0; w < 8; w++) {
-      const float v = cand_v[w * M + tid];
-      const int n = cand_n[w * M + tid];
-      if (v > cv || (v == cv && n < cn)) { cv = v; cn = n; }
+    for (int m = 0; m < M; m++) {
+      if (bn[m] != 0x7fffffff) {
+        const unsigned int b = __float_as_uint(bv[m]);
+        const unsigned int ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+        atomicMax(&gp.keys[m], ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (unsigned int)bn[m]));
+      }
     }
   }
-  greedy_pick_finish<M>(gp, cv, cn);
+  if (gp.next_w != nullptr && tid == 32) {  // this CTA's share of the next kernel's weights, towards L2
+    const unsigned int n16 = gp.next_w_bytes >> 4;
+    const unsigned int beg = (unsigned int)(((unsigned long long)n16 * blockIdx.x) / gridDim.x);
+    const unsigned int end = (unsigned int)(((unsigned long long)n16 * (blockIdx.x + 1)) / gridDim.x);
+    for (unsigned int o = beg; o < end; o += 1024u)
+      prefetch_l2(gp.next_w + ((size_t)o << 4), min(end - o, 1024u) << 4);
+  }
+  __shared__ unsigned int is_last;
+  __syncthreads();  // every warp of this CTA has made its last request and its last update of the keys
+  if (tid == 0) {
+    __threadfence();
+    is_last = (atomicAdd(&work[1], 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  int my_step = 0;
+  if (gp.keys != nullptr && tid < M) {
+    const unsigned long long key = atomicExch(&gp.keys[tid], 0ull);
+    const unsigned int idx = key ? 0xffffffffu - (unsigned int)(key & 0xffffffffull) : 0u;
+    my_step = __ldcg(gp.step);
+    gp.next_ids[tid] = idx;
+    if (gp.out_ids) gp.out_ids[(size_t)tid * gp.out_stride + my_step] = idx;
+  }
+  __syncthreads();  // every row has read the step counter
+  if (tid == 0) {
+    work[0] = 0u;
+    work[1] = 0u;
+    if (gp.keys != nullptr) {
+      *gp.pos = __ldcg(gp.pos) + gp.n_tok;
+      *gp.step = my_step + 1;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
