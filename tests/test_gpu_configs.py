@@ -191,3 +191,67 @@ def test_gpt2_xl_full_depth(oracle):
         assert rel_err(step, again) < TF32X3
     finally:
         gpt.destroy()
+
+
+def wide_vocab_params(n_embd=384, n_head=6, n_layer=1):
+    """A shallow model with the full 50257-token vocabulary: the de-embedding matrix is larger than L2, so the pass
+    ends in the looping de-embedding kernel (resident CTAs, dynamically assigned column chunks, greedy pick through
+    atomic-max keys) exactly as the 117M model's does, while the oracle stays fast."""
+    p = dict(synth.CONFIGS["gpt2"])
+    p.update(n_embd=n_embd, n_head=n_head, n_layer=n_layer, n_ctx=64)
+    return p
+
+
+@pytest.mark.parametrize("n_seq", [1, 2, 3, 5, 8])
+def test_full_vocabulary_deembedding_rows(oracle, n_seq):
+    """1..8 sequences against the full-vocabulary de-embedding (one CTA-resident kernel instance per row count):
+    greedy ids of every sequence and the last step's logits, model.js:224-229 + globals.js:66-74."""
+    params = wide_vocab_params()
+    w = synth.make_weights(params, seed=77)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    n_prompt, n_new = 9, 6
+    prompts = np.stack([synth.make_tokens(params["vocab_size"], n_prompt, seed=3, stream=50 + i) for i in range(n_seq)])
+    gpt = make_gpt(params, w)
+    try:
+        got = gpt.session(n_seq).generate_greedy(prompts, n_new)
+        for i in range(n_seq):
+            want = m.kv_generate_greedy(prompts[i], n_new)
+            ref = m.kv_logits(np.concatenate([prompts[i], want])[:-1])
+            assert_ids_equal_up_to_near_tie(got[i], want, lambda k: ref[n_prompt - 1 + k], f"{n_seq} rows, sequence {i}")
+        s = gpt.session(n_seq)
+        s.reset()
+        s.forward(prompts, want_logits=False)
+        for t in range(n_new - 2):
+            s.forward(got[:, t:t + 1], want_logits=False)
+        lg = s.forward(got[:, n_new - 2:n_new - 1])
+        for i in range(n_seq):
+            ref = m.kv_logits(np.concatenate([prompts[i], got[i, :n_new - 1]]))[-1]
+            assert rel_err(lg[i], ref) < TIGHT, i
+    finally:
+        gpt.destroy()
+
+
+def test_greedy_pick_ties_take_the_lowest_index(oracle):
+    """Equal logits: the reference sorts (value, index) pairs and takes the first (globals.js:66-74), i.e. the lowest
+    index wins. Rows of the tied de-embedding matrix are duplicated so that the best logit of the first generated
+    token occurs three times, in chunks handled by different warps and CTAs."""
+    params = wide_vocab_params()
+    w = synth.make_weights(params, seed=78)
+    prompt = synth.make_tokens(params["vocab_size"], 12, seed=4)
+    m0 = oracle.Model(params, synth.weight_list(params, w))
+    best = int(m0.kv_generate_greedy(prompt, 1)[0])
+    wte = w["transformer.wte.weight"]
+    lo, hi = 11, 50001
+    assert lo not in prompt and hi not in prompt and lo < best < hi
+    wte[lo] = wte[best]
+    wte[hi] = wte[best]
+    m = oracle.Model(params, synth.weight_list(params, w))
+    want = m.kv_generate_greedy(prompt, 4)
+    assert int(want[0]) == lo
+    gpt = make_gpt(params, w)
+    try:
+        got = gpt.session().generate_greedy(prompt, 4)[0]
+        assert int(got[0]) == lo
+        assert np.array_equal(got, want)
+    finally:
+        gpt.destroy()
