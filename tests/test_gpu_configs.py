@@ -202,11 +202,12 @@ def wide_vocab_params(n_embd=384, n_head=6, n_layer=1):
     return p
 
 
-@pytest.mark.parametrize("n_seq", [1, 2, 3, 5, 8])
-def test_full_vocabulary_deembedding_rows(oracle, n_seq):
-    """1..8 sequences against the full-vocabulary de-embedding (one CTA-resident kernel instance per row count):
-    greedy ids of every sequence and the last step's logits, model.js:224-229 + globals.js:66-74."""
-    params = wide_vocab_params()
+@pytest.mark.parametrize("n_seq,n_layer", [(1, 1), (2, 3), (3, 2), (4, 3), (5, 1), (7, 2), (8, 3)])
+def test_full_vocabulary_deembedding_rows(oracle, n_seq, n_layer):
+    """1..8 sequences in lockstep through 1..3 blocks, ending in the full-vocabulary de-embedding (one CTA-resident
+    kernel instance per row count): greedy ids of every sequence and the last step's logits, model.js:104-229 +
+    globals.js:66-74."""
+    params = wide_vocab_params(n_layer=n_layer)
     w = synth.make_weights(params, seed=77)
     m = oracle.Model(params, synth.weight_list(params, w))
     n_prompt, n_new = 9, 6
