@@ -92,9 +92,10 @@ __device__ __forceinline__ float4 warp_rows_partial(const float4 *__restrict__ b
 // halfwarp_rows_sum: lanes 0..15 and 16..31 of a warp are the same 16 columns (col16 = lane & 15) and take the even
 // and the odd rows (at most MAXR each); the two halves are combined with one shuffle. Every lane of the warp must
 // call it; returns the sum of all rows for the lane's column (the same value in both halves).
-template <int MAXR>
+// `between` runs once the loads have been issued and before the first of them is waited for.
+template <int MAXR, typename Between>
 __device__ __forceinline__ float4 halfwarp_rows_sum(const float4 *__restrict__ base, int ncols, size_t stride4,
-                                                    int n_rows, int lane) {
+                                                    int n_rows, int lane, Between between) {
   const int c = lane & 15, half = lane >> 4;
   float4 v[MAXR];
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -105,11 +106,14 @@ __device__ __forceinline__ float4 halfwarp_rows_sum(const float4 *__restrict__ b
       const int r = half + 2 * k;
       v[k] = ldcg_pinned(base + (size_t)(r < n_rows ? r : 0) * stride4 + cc);
     }
+    between();
 #pragma unroll
     for (int k = 0; k < MAXR; k++) pin4(v[k]);
 #pragma unroll
     for (int k = 0; k < MAXR; k++)
       if (c < ncols && half + 2 * k < n_rows) a = add4(a, v[k]);
+  } else {
+    between();
   }
   a.x += __shfl_xor_sync(0xffffffffu, a.x, 16);
   a.y += __shfl_xor_sync(0xffffffffu, a.y, 16);
@@ -575,7 +579,6 @@ mlp_block_kernel(MlpBlockParams p) {
   cluster_arrive();  // pairs with the wait below: every CTA of the cluster is running before any remote store
   if (tid == 0) {
     bulk_g2s_block(wfc, p.wfc_t + (size_t)j0 * E, (uint32_t)nu * (uint32_t)E * 4u, &bars[0]);
-    bulk_g2s_block(wdn, p.wpr_kn + (size_t)j0 * E, (uint32_t)nu * (uint32_t)E * 4u, &bars[1]);
   }
   pdl_wait();
   trace(9, 1);
@@ -587,8 +590,15 @@ mlp_block_kernel(MlpBlockParams p) {
     const int cbase = (int)rank * nq4;
     const int c = warp * 16 + (lane & 15);  // one warp per 16 columns, its two halves take alternate rows
     const bool mine = c < nq4 && lane < 16;
-    const float4 sum = halfwarp_rows_sum<kMlpSumRows>(reinterpret_cast<const float4 *>(p.part_in) + cbase + warp * 16,
-                                                     min(16, max(nq4 - warp * 16, 0)), (size_t)E4, p.n_part, lane);
+    // The second weight block is requested only here, behind this kernel's own loads of the partial results: requested
+    // ahead of the wait together with the first, its 9.4 MB were still arriving when these loads were issued, and they
+    // waited behind it (2.9 us instead of 1.6 us from the wait to the exchange).
+    const float4 sum = halfwarp_rows_sum<kMlpSumRows>(
+        reinterpret_cast<const float4 *>(p.part_in) + cbase + warp * 16, min(16, max(nq4 - warp * 16, 0)), (size_t)E4,
+        p.n_part, lane, [&] {
+          if (tid == 0)
+            bulk_g2s_block(wdn, p.wpr_kn + (size_t)j0 * E, (uint32_t)nu * (uint32_t)E * 4u, &bars[1]);
+        });
     float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f);
     x_col = cbase + c;
     if (mine)
