@@ -625,7 +625,7 @@ struct SplitHandoff {
 // C = A[M,K] (row stride lda) . Wt[N,K]^T on the tensor cores; x3 selects 3 x TF32.
 static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t lda, const float *Wt, int M, int K,
                               int N, const Epilogue &epi, LnAfter *ln = nullptr, bool b_static = true,
-                              const float *Wt_lo = nullptr, SplitHandoff *handoff = nullptr) {
+                              const float *Wt_lo = nullptr, SplitHandoff *handoff = nullptr, bool b_exact = false) {
   REQUIRE(aligned16(A) && aligned16(Wt) && (lda % 4) == 0 && (K % 4) == 0, WGPT_ERR_ALIGN,
           "tensor-core GEMM operands must be 16-byte aligned with row strides that are multiples of 16 bytes");
   CUtensorMap ma, mb;
@@ -703,7 +703,8 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
     auto kern = gemm_tc_kernel<true>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<true>::kSmemBytes));
     LAUNCH_PDL(dev, kern, grid, TcPlan<true>::kThreads, TcPlan<true>::kSmemBytes, m_first, m_second, mlo, km, K, kn,
-               epi, dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0, lo_tma ? 1 : 0);
+               epi, dev->d_err, kb_per_split, splits, split_out, static_op, exchanged ? 1 : 0,
+               lo_tma ? 1 : (b_exact && !exchanged ? 2 : 0));
   } else {
     auto kern = gemm_tc_kernel<false>;
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcPlan<false>::kSmemBytes));
@@ -1110,7 +1111,9 @@ WGPT_EXPORT int32_t wgpt_int8_matmul(wgpt_device *dev, int32_t M, int32_t K, int
       dim3 xgrid((N / 4 + 31) / 32, (K + 31) / 32);
       LAUNCH(dev, int8_expand_nk_kernel, xgrid, 256, 0, Bq, K, N, wt);
       // the expanded weight was written by the kernel just before: no reads of it ahead of the dependency wait
-      return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false);
+      // the expanded codes are integers: exact in TF32, no low part
+      return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false,
+                            nullptr, nullptr, true);
     }
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     LAUNCH(dev, int8_gemm_simt_kernel, grid, 256, 0, A, Bq, M, K, N, e);
@@ -1233,7 +1236,8 @@ WGPT_EXPORT int32_t wgpt_int8_matmul_w(wgpt_device *dev, int32_t M, const wgpt_i
     LAUNCH(dev, int8_expand_bytes_kernel, grid_for(n16, 256, dev->sm_count), 256, 0, (const uint8_t *)w->bytes, n16, wt);
     Epilogue e = plain_epi(out, N, nullptr);
     e.colscale = w->scale;
-    return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false);
+    return launch_gemm_tc(dev, dev->precision == WGPT_PRECISION_TF32X3, A, (size_t)K, wt, M, K, N, e, nullptr, false,
+                          nullptr, nullptr, true);
   }
   return wgpt_int8_matmul(dev, M, K, N, A, w->words, w->scale, out);
 }

@@ -165,7 +165,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int n_work = m_tiles * n_tiles * splits;
   // 3xTF32 with the weight operand's low part precomputed in HBM (map_b_lo): TMA brings it into the stage's B-lo
   // slot and the split warps only treat the A tile. Requires B to be the static operand or no early loads.
-  const bool lo_tma = X3 && b_lo_tma != 0;
+  // b_lo_tma == 2: the weight operand is exact in TF32 (small integers, the int8 codes): it has no low part, so its
+  // tile is not split and the a_hi x b_lo product is not issued (two MMAs per k-step instead of three).
+  const bool lo_tma = X3 && b_lo_tma == 1;
+  const bool b_exact = X3 && b_lo_tma == 2;
 #ifdef WGPT_TRACE
   __shared__ unsigned int tc_trace_base;  // the roles below are different threads: they share thread 0's record
   {
@@ -271,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (X3) {
               const uint64_t dal = umma_desc_sw128(a_hi + 2 * TC_TILE_BYTES + k * 32);
               const uint64_t dbl = umma_desc_sw128(b_hi + 2 * TC_TILE_BYTES + k * 32);
-              umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
+              if (!b_exact) umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
               umma_tf32(tmem_acc, dal, db, TC_IDESC, 1u);
             }
           }
@@ -406,7 +409,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lo = hi + 2 * TC_TILE_BYTES;
 #pragma unroll 8
         for (int q = 0; q < (2 * TC_TILE_BYTES) / (16 * 128); q++) {
-          if (lo_tma && q == TC_TILE_BYTES / (16 * 128)) break;  // the B tile's low part came by TMA
+          if ((lo_tma || b_exact) && q == TC_TILE_BYTES / (16 * 128)) break;  // the B tile's low part came by TMA, or is zero
           // kind::tf32 reads the top 19 bits of each FP32 operand and ignores the rest (checked on B200: clearing
           // the low 13 bits first gives bit-identical products), so the staged tile itself serves as `hi`.
           float4 x = lds128(hi + (uint32_t)q * 2048u), l;
