@@ -44,7 +44,9 @@ def test_bpe_merges_in_rank_order_and_round_trips():
 
 
 def test_published_gpt2_merges_when_available():
-    folder = "/root/reference/weights/tokenization"
+    # a checkout of the reference beside this repository, if there is one
+    here = os.path.dirname(os.path.abspath(__file__))
+    folder = os.path.join(os.path.dirname(os.path.dirname(here)), "reference", "weights", "tokenization")
     if not os.path.exists(os.path.join(folder, "vocab.bpe")):
         pytest.skip("no GPT-2 merge list on this machine")
     t = GPT2Tokenizer().load(folder)
