@@ -73,6 +73,20 @@ __device__ __forceinline__ float4 epi_apply4(const Epilogue &e, float4 v, int m,
   return v;
 }
 
+// epi_apply4 with the bias and the residual already in registers (zero where the epilogue has none): a second stage
+// fetches the bias ahead of its dependency wait and requests the residual together with its partial sums instead
+// of one memory round trip later.
+__device__ __forceinline__ float4 epi_apply4_pre(const Epilogue &e, float4 v, float4 bias, float4 res, int n) {
+  if (e.colscale) {
+    float4 c = *reinterpret_cast<const float4 *>(e.colscale + n);
+    v.x *= c.x; v.y *= c.y; v.z *= c.z; v.w *= c.w;
+  }
+  v.x += bias.x; v.y += bias.y; v.z += bias.z; v.w += bias.w;
+  if (e.act == 1) { v.x = gelu_f(v.x); v.y = gelu_f(v.y); v.z = gelu_f(v.z); v.w = gelu_f(v.w); }
+  v.x += res.x; v.y += res.y; v.z += res.z; v.w += res.w;
+  return v;
+}
+
 __device__ __forceinline__ void epi_store4(const Epilogue &e, float4 v, int m, int n) {
   *reinterpret_cast<float4 *>(epi_addr(e, m, n)) = epi_apply4(e, v, m, n);
 }

@@ -832,11 +832,15 @@ __global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit
   int N4 = N >> 2;
   TRACE_BEGIN(6);
   trace(6, 0);
+  const bool live = i < M * N4;
+  const int m = live ? i / N4 : 0, n = live ? (i - m * N4) * 4 : 0;
+  float4 bias_pre = make_float4(0.f, 0.f, 0.f, 0.f), res_pre = bias_pre;
+  if (live && epi.bias) bias_pre = *reinterpret_cast<const float4 *>(epi.bias + n);  // a weight: ahead of the wait
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the previous kernel
   trace(6, 1);
-  if (i >= M * N4) return;
-  int m = i / N4, n = (i - m * N4) * 4;
+  if (!live) return;
+  if (epi.residual) res_pre = __ldcg(reinterpret_cast<const float4 *>(epi.residual + (size_t)m * epi.ld + n));
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   const int n_tiles = (N + tw - 1) / tw, nt = n / tw;
   const float *p0 = part + ((size_t)nt * M + m) * tw + (n - nt * tw);
@@ -846,7 +850,7 @@ __global__ void gemv_kn_reduce_kernel(const float *__restrict__ part, int ksplit
     float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
-  epi_store4(epi, s, m, n);
+  *reinterpret_cast<float4 *>(epi_addr(epi, m, n)) = epi_apply4_pre(epi, s, bias_pre, res_pre, n);
   trace(6, 2);
 }
 
@@ -864,9 +868,29 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
   const int N4 = N >> 2;
   TRACE_BEGIN(7);
   trace(7, 0);
+  // weights (LayerNorm scale and shift, bias) ahead of the dependency wait; the residual with the partial sums
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 g_pre[kReduceLnVec], b_pre[kReduceLnVec], bias_pre[kReduceLnVec], res_pre[kReduceLnVec];
+#pragma unroll
+  for (int r = 0; r < kReduceLnVec; r++) {
+    const int i = tid + 256 * r;
+    g_pre[r] = b_pre[r] = bias_pre[r] = res_pre[r] = zero4;
+    if (i < N4) {
+      g_pre[r] = *reinterpret_cast<const float4 *>(gamma + 4 * i);
+      b_pre[r] = *reinterpret_cast<const float4 *>(beta + 4 * i);
+      if (epi.bias) bias_pre[r] = *reinterpret_cast<const float4 *>(epi.bias + 4 * i);
+    }
+  }
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the previous kernel
   trace(7, 1);
+  if (epi.residual) {
+#pragma unroll
+    for (int r = 0; r < kReduceLnVec; r++) {
+      const int i = tid + 256 * r;
+      if (i < N4) res_pre[r] = __ldcg(reinterpret_cast<const float4 *>(epi.residual + (size_t)m * epi.ld + 4 * i));
+    }
+  }
   float4 v[kReduceLnVec];
   float s = 0.f;
 #pragma unroll
@@ -899,7 +923,7 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
         float4 t = __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)k * zstride));
         a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
       }
-      a = epi_apply4(epi, a, m, n);
+      a = epi_apply4_pre(epi, a, bias_pre[r], res_pre[r], n);
       *reinterpret_cast<float4 *>(epi_addr(epi, m, n)) = a;
       v[r] = a;
       s += (a.x + a.y) + (a.z + a.w);
@@ -931,7 +955,7 @@ splitk_reduce_ln_kernel(const float *__restrict__ part, int ksplit, int M, int N
   for (int r = 0; r < kReduceLnVec; r++) {
     const int i = tid + 256 * r;
     if (i < N4) {
-      float4 g = *reinterpret_cast<const float4 *>(gamma + 4 * i), b = *reinterpret_cast<const float4 *>(beta + 4 * i);
+      const float4 g = g_pre[r], b = b_pre[r];
       *reinterpret_cast<float4 *>(ln_out + (size_t)m * N + 4 * i) =
           make_float4(g.x * ((v[r].x - mean) / sd) + b.x, g.y * ((v[r].y - mean) / sd) + b.y,
                       g.z * ((v[r].z - mean) / sd) + b.z, g.w * ((v[r].w - mean) / sd) + b.w);
