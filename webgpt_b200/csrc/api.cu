@@ -1261,6 +1261,7 @@ struct FusedPlan {
   size_t smem_a = 0;
   int units = 0, n_mlp = 0 /* CTAs */, n_mlp_rows = 0 /* clusters = partial rows */, wk = 0, down_parts = 0, red_b = 0;
   size_t smem_b = 0;
+  int attn_extra = 0;      // clusters of attn_block_kernel beyond the heads that prefetch the MLP kernel's weights
 };
 
 struct wgpt_model {
@@ -1425,7 +1426,8 @@ static int32_t attn_block_launch_t(wgpt_device *dev, const FusedPlan &fp, int H,
     CK(cudaOccupancyMaxActiveClusters(max_clusters, kern, &cfg));
     return WGPT_OK;
   }
-  CK(launch_cluster_x(dev->pdl, CS, dev->stream, kern, dim3(H * CS), dim3(kAttnBlockThreads), fp.smem_a, a));
+  const int extra = a.pf_a != nullptr ? fp.attn_extra : 0;  // clusters that only prefetch for the next kernel
+  CK(launch_cluster_x(dev->pdl, CS, dev->stream, kern, dim3((H + extra) * CS), dim3(kAttnBlockThreads), fp.smem_a, a));
   dev->launches++;
   return WGPT_OK;
 }
@@ -1533,6 +1535,11 @@ static int32_t fused_plan(wgpt_model *m) {
               max_clusters, H);
     if (max_clusters < H) continue;
     fp.ok = true;
+    {  // two more clusters when they are resident together with the heads' and SMs are left over for them
+      const char *ev = getenv("WGPT_ATTN_EXTRA");
+      const int want = ev ? atoi(ev) : 2;
+      fp.attn_extra = (max_clusters >= H + want && (H + want) * cs <= dev->sm_count && want >= 2) ? want : 0;
+    }
     break;
   }
   return WGPT_OK;
@@ -1747,6 +1754,10 @@ static int32_t forward_blocks_fused(wgpt_session *s, const uint32_t *ids) {
     a.E = E; a.H = H; a.scale = m->scale;
     a.proj_parts = fp.proj_parts; a.red_floats = fp.red_a;
     a.err = dev->d_err;
+    if (fp.attn_extra > 0) {  // the MLP kernel's weights, for the clusters beyond the heads
+      a.pf_a = reinterpret_cast<const char *>(L.wfc_t); a.pf_b = reinterpret_cast<const char *>(L.wpr_kn);
+      a.pf_bytes = (unsigned int)((size_t)F * E * 4);
+    }
     TRY(attn_block_launch(dev, fp, m->hs, H, a));
     MlpBlockParams b;
     memset(&b, 0, sizeof b);
