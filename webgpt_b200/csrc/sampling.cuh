@@ -56,13 +56,23 @@ sample_topk_kernel(const float *__restrict__ logits, int V, int top_k, double te
 
   unsigned long long best = 0ull;  // below every real key (their low word is never zero for idx < 2^32 - 1)
   {
-    int i = tid;  // eight loads in flight per thread: one CTA scans the row, so latency is what bounds it
-    for (; i + 7 * kSampleThreads < V; i += 8 * kSampleThreads) {
-      float f[8];
+    int i = tid;  // 16 loads in flight per thread: one CTA scans the row, so latency is what bounds it
+    for (; i + 15 * kSampleThreads < V; i += 16 * kSampleThreads) {
+      float f[16];
 #pragma unroll
-      for (int u = 0; u < 8; u++) f[u] = __ldcg(x + i + u * kSampleThreads);
+      for (int u = 0; u < 16; u++) f[u] = __ldcg(x + i + u * kSampleThreads);
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
+      for (int u = 0; u < 16; u++) {
+        unsigned long long c = sample_key(f[u], i + u * kSampleThreads);
+        best = c > best ? c : best;
+      }
+    }
+    for (; i + 3 * kSampleThreads < V; i += 4 * kSampleThreads) {
+      float f[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) f[u] = __ldcg(x + i + u * kSampleThreads);
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
         unsigned long long c = sample_key(f[u], i + u * kSampleThreads);
         best = c > best ? c : best;
       }
@@ -88,8 +98,22 @@ sample_topk_kernel(const float *__restrict__ logits, int V, int top_k, double te
     }
   }
   const unsigned long long tau = srt[top_k - 1];
-  if (best >= tau && best != 0ull) {
-    for (int i = tid; i < V; i += kSampleThreads) {
+  if (best >= tau && best != 0ull) {  // at most top_k threads: their share again, 16 loads at a time
+    int i = tid;
+    for (; i + 15 * kSampleThreads < V; i += 16 * kSampleThreads) {
+      float f[16];
+#pragma unroll
+      for (int u = 0; u < 16; u++) f[u] = __ldcg(x + i + u * kSampleThreads);
+#pragma unroll
+      for (int u = 0; u < 16; u++) {
+        unsigned long long c = sample_key(f[u], i + u * kSampleThreads);
+        if (c >= tau) {
+          int slot = atomicAdd(&s_cnt, 1);
+          if (slot < cap) cand[slot] = c;
+        }
+      }
+    }
+    for (; i < V; i += kSampleThreads) {
       unsigned long long c = sample_key(__ldcg(x + i), i);
       if (c >= tau) {
         int slot = atomicAdd(&s_cnt, 1);
