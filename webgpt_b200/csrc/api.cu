@@ -832,6 +832,19 @@ static int32_t launch_attn_prefill(wgpt_device *dev, int hs, const float *q, int
                                    int ldkv, size_t kv_seq_stride, float *out, int ldo, int n_tok, int n_seq, int H,
                                    const int *pos, float scale) {
   static const bool tiled64 = [] { const char *ev = getenv("WGPT_ATTN_PREFILL64"); return !(ev && ev[0] == '0'); }();
+  static const bool mma64 = [] { const char *ev = getenv("WGPT_ATTN_PREFILL_MMA"); return !(ev && ev[0] == '0'); }();
+  if (hs == 64 && mma64 && dev->precision != WGPT_PRECISION_FP32 && n_tok >= 16 && (ldq % 4) == 0 && (ldkv % 4) == 0 &&
+      (ldo % 2) == 0) {
+    // products in TF32 / 3xTF32: the warp-level tensor-core kernel; FP32 mode keeps the CUDA-core kernels below
+    dim3 grid((n_tok + 63) / 64, H, n_seq);
+    if (dev->precision == WGPT_PRECISION_TF32X3)
+      LAUNCH(dev, attn_prefill64_mma_kernel<true>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok, pos,
+             scale);
+    else
+      LAUNCH(dev, attn_prefill64_mma_kernel<false>, grid, 128, 0, q, ldq, kc, vc, ldkv, kv_seq_stride, out, ldo, n_tok,
+             pos, scale);
+    return WGPT_OK;
+  }
   if (hs == 64 && tiled64 && n_tok >= 16 && (ldq % 4) == 0 && (ldkv % 4) == 0 && (ldo % 4) == 0) {
     const size_t smem = attn_prefill64_smem_bytes();
     CK(cudaFuncSetAttribute(attn_prefill64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

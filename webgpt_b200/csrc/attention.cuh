@@ -438,3 +438,175 @@ attn_prefill64_kernel(const float *__restrict__ q, int ldq, const float *__restr
 }
 
 }  // namespace wgpt
+
+namespace wgpt {
+
+// ------------------------------------------------------------------------------------------------
+// Prefill for head size 64 on the tensor cores (warp-level mma.sync.m16n8k8, TF32 inputs, FP32 accumulation), used
+// when the device computes products in TF32 or 3xTF32; the FP32 mode keeps attn_prefill64_kernel. A CTA of four
+// warps takes 64 query rows (16 per warp) against key tiles of 64 held in shared memory; scores, online softmax and
+// the probabilities never leave registers (the accumulator fragment of the score product is re-arranged into the
+// A fragment of the value product with shuffles inside each quad of lanes). X3: every operand is split into
+// hi = its top 19 bits and lo = x - hi, and each product is hi*hi + hi*lo + lo*hi, as in the GEMM kernels.
+// Same mathematics as attn_prefill64_kernel (instructions.js:1101-1214, :593-666); masked keys contribute zero.
+constexpr int kAttnMmaKLd = 68, kAttnMmaVLd = 72;  // row strides (floats) that keep the fragment loads conflict-free
+
+__device__ __forceinline__ void mma_tf32_16x8x8(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t tf32_hi_bits(float x) { return __float_as_uint(x) & 0xFFFFE000u; }
+__device__ __forceinline__ uint32_t tf32_lo_bits(float x) {
+  return __float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
+}
+
+template <bool X3>
+__global__ void __launch_bounds__(128)
+attn_prefill64_mma_kernel(const float *__restrict__ q, int ldq, const float *__restrict__ kc,
+                          const float *__restrict__ vc, int ldkv, size_t kv_seq_stride, float *__restrict__ out,
+                          int ldo, int n_tok, const int *__restrict__ pos, float scale) {
+  constexpr int HS = 64, T = 64, KLD = kAttnMmaKLd, VLD = kAttnMmaVLd;
+  __shared__ __align__(16) float Ks[T * KLD];
+  __shared__ __align__(16) float Vs[T * VLD];
+  const int h = blockIdx.y, seq = blockIdx.z, t0 = blockIdx.x * T;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int pos0 = pos ? *pos : 0;
+  const int nq = min(T, n_tok - t0);
+  const int last_key = pos0 + t0 + nq - 1;  // newest key any query of this tile may see
+  const int r0 = 16 * warp + g, r1 = r0 + 8;  // this lane's two query rows inside the tile
+  const int p0 = pos0 + t0 + min(r0, nq - 1), p1 = pos0 + t0 + min(r1, nq - 1);  // rows past the end shadow the last
+  const int warp_last = pos0 + t0 + min(16 * warp + 15, nq - 1);
+
+  // ---- Q fragments (A operand of the score product), staged through the K buffer
+  for (int idx = tid; idx < T * (HS / 4); idx += 128) {
+    const int r = idx >> 4, c4 = (idx & 15) * 4;
+    const int tq = t0 + min(r, nq - 1);
+    *reinterpret_cast<float4 *>(Ks + r * KLD + c4) =
+        *reinterpret_cast<const float4 *>(q + ((size_t)seq * n_tok + tq) * ldq + h * HS + c4);
+  }
+  __syncthreads();
+  uint32_t qh[8][4], ql[X3 ? 8 : 1][4];
+#pragma unroll
+  for (int ks = 0; ks < 8; ks++) {
+    const float x0 = Ks[r0 * KLD + 8 * ks + t], x1 = Ks[r1 * KLD + 8 * ks + t];
+    const float x2 = Ks[r0 * KLD + 8 * ks + t + 4], x3 = Ks[r1 * KLD + 8 * ks + t + 4];
+    qh[ks][0] = tf32_hi_bits(x0); qh[ks][1] = tf32_hi_bits(x1); qh[ks][2] = tf32_hi_bits(x2); qh[ks][3] = tf32_hi_bits(x3);
+    if (X3) {
+      ql[ks][0] = tf32_lo_bits(x0); ql[ks][1] = tf32_lo_bits(x1); ql[ks][2] = tf32_lo_bits(x2); ql[ks][3] = tf32_lo_bits(x3);
+    }
+  }
+  const float *kb = kc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+  const float *vb = vc + (size_t)seq * kv_seq_stride * ldkv + h * HS;
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+
+  for (int j0 = 0; j0 <= last_key; j0 += T) {
+    __syncthreads();  // the previous tile (or the staged Q) is no longer read
+    for (int idx = tid; idx < T * (HS / 4); idx += 128) {
+      const int r = idx >> 4, c4 = (idx & 15) * 4;
+      const int j = min(j0 + r, last_key);
+      *reinterpret_cast<float4 *>(Ks + r * KLD + c4) = *reinterpret_cast<const float4 *>(kb + (size_t)j * ldkv + c4);
+      *reinterpret_cast<float4 *>(Vs + r * VLD + c4) = *reinterpret_cast<const float4 *>(vb + (size_t)j * ldkv + c4);
+    }
+    __syncthreads();
+    if (j0 > warp_last) continue;  // every key of the tile is masked for this warp's rows (same for the whole warp)
+
+    // ---- scores: 16 rows x 64 keys as eight 16x8 accumulators
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) {
+        const float k0 = Ks[(8 * j + g) * KLD + 8 * ks + t], k1 = Ks[(8 * j + g) * KLD + 8 * ks + t + 4];
+        const uint32_t kh0 = tf32_hi_bits(k0), kh1 = tf32_hi_bits(k1);
+        mma_tf32_16x8x8(s[j], qh[ks], kh0, kh1);
+        if (X3) {
+          mma_tf32_16x8x8(s[j], qh[ks], tf32_lo_bits(k0), tf32_lo_bits(k1));
+          mma_tf32_16x8x8(s[j], ql[ks], kh0, kh1);
+        }
+      }
+    }
+    // ---- online softmax of rows r0 (elements 0, 1) and r1 (elements 2, 3); key of element e: j0 + 8j + 2t + (e & 1)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int key = j0 + 8 * j + 2 * t + (e & 1);
+        const int pq = e < 2 ? p0 : p1;
+        s[j][e] = key <= pq ? s[j][e] * scale : -INFINITY;
+      }
+      mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = (m0 == -INFINITY) ? 0.f : expf(m0 - mn0), c1 = (m1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      s[j][0] = (s[j][0] == -INFINITY) ? 0.f : expf(s[j][0] - mn0);
+      s[j][1] = (s[j][1] == -INFINITY) ? 0.f : expf(s[j][1] - mn0);
+      s[j][2] = (s[j][2] == -INFINITY) ? 0.f : expf(s[j][2] - mn1);
+      s[j][3] = (s[j][3] == -INFINITY) ? 0.f : expf(s[j][3] - mn1);
+      ps0 += s[j][0] + s[j][1];
+      ps1 += s[j][2] + s[j][3];
+    }
+    if (mn0 != -INFINITY) { l0 = l0 * c0 + ps0; m0 = mn0; }  // l holds this lane's share of the row sum
+    if (mn1 != -INFINITY) { l1 = l1 * c1 + ps1; m1 = mn1; }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1;
+    }
+    // ---- values: the probabilities of keys 8ks..8ks+7 become the A fragment of k-step ks
+    const int src_lo = (lane & ~3) | (t >> 1), src_hi = src_lo + 2;
+    const bool odd = (t & 1) != 0;
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+      // element (row, key 8ks + c) sits in the lane of the quad with 2*tig == c & ~1, as element c & 1 (row r0) / 2 + (c & 1) (row r1)
+      const float e0a = __shfl_sync(0xffffffffu, s[ks][0], src_lo), e1a = __shfl_sync(0xffffffffu, s[ks][1], src_lo);
+      const float e2a = __shfl_sync(0xffffffffu, s[ks][2], src_lo), e3a = __shfl_sync(0xffffffffu, s[ks][3], src_lo);
+      const float e0b = __shfl_sync(0xffffffffu, s[ks][0], src_hi), e1b = __shfl_sync(0xffffffffu, s[ks][1], src_hi);
+      const float e2b = __shfl_sync(0xffffffffu, s[ks][2], src_hi), e3b = __shfl_sync(0xffffffffu, s[ks][3], src_hi);
+      const float a0 = odd ? e1a : e0a, a1 = odd ? e3a : e2a;  // keys 8ks + t of rows r0, r1
+      const float a2 = odd ? e1b : e0b, a3 = odd ? e3b : e2b;  // keys 8ks + t + 4
+      uint32_t ph[4] = {tf32_hi_bits(a0), tf32_hi_bits(a1), tf32_hi_bits(a2), tf32_hi_bits(a3)};
+      uint32_t pl[4] = {0u, 0u, 0u, 0u};
+      if (X3) { pl[0] = tf32_lo_bits(a0); pl[1] = tf32_lo_bits(a1); pl[2] = tf32_lo_bits(a2); pl[3] = tf32_lo_bits(a3); }
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float v0 = Vs[(8 * ks + t) * VLD + 8 * j + g], v1 = Vs[(8 * ks + t + 4) * VLD + 8 * j + g];
+        const uint32_t vh0 = tf32_hi_bits(v0), vh1 = tf32_hi_bits(v1);
+        mma_tf32_16x8x8(o[j], ph, vh0, vh1);
+        if (X3) {
+          mma_tf32_16x8x8(o[j], ph, tf32_lo_bits(v0), tf32_lo_bits(v1));
+          mma_tf32_16x8x8(o[j], pl, vh0, vh1);
+        }
+      }
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if (r0 < nq)
+      *reinterpret_cast<float2 *>(out + ((size_t)seq * n_tok + t0 + r0) * ldo + h * HS + 8 * j + 2 * t) =
+          make_float2(o[j][0] * i0, o[j][1] * i0);
+    if (r1 < nq)
+      *reinterpret_cast<float2 *>(out + ((size_t)seq * n_tok + t0 + r1) * ldo + h * HS + 8 * j + 2 * t) =
+          make_float2(o[j][2] * i1, o[j][3] * i1);
+  }
+}
+
+}  // namespace wgpt
