@@ -389,3 +389,31 @@ def test_sharded_generation_inside_the_library_equals_unsharded(oracle):
     finally:
         multi.destroy()
         single.destroy()
+
+
+@pytest.mark.parametrize("precision,tol", [("tf32x3", 5e-5), ("tf32", 5e-3), ("fp32", 5e-5)])
+def test_prefill_attention_head64_chunked(oracle, precision, tol):
+    """Prefill attention for head size 64 (tensor-core kernel in the TF32 modes, CUDA-core kernel in FP32): windows of
+    16..129 tokens appended to a cache that already holds earlier positions, with partial last tiles, against one
+    oracle pass over the whole window (instructions.js:1101-1214: causal mask by absolute position)."""
+    from webgpt_b200 import _lib
+    params = dict(synth.CONFIGS["small"])
+    params.update(n_embd=128, n_head=2, n_layer=2, n_ctx=256, vocab_size=96)
+    w = synth.make_weights(params, seed=31, std=0.08, ln_random=True)
+    m = oracle.Model(params, synth.weight_list(params, w))
+    ids = synth.make_tokens(params["vocab_size"], 230, seed=9)
+    ref = m.kv_logits(ids)  # ref[t] = logits after feeding ids[0..t]
+    gpt = make_gpt(params, w)
+    try:
+        gpt.device.set_precision({"fp32": _lib.PRECISION_FP32, "tf32x3": _lib.PRECISION_TF32X3,
+                                  "tf32": _lib.PRECISION_TF32}[precision])
+        s = gpt.session()
+        for chunks in ([230], [16, 129, 65, 20], [100, 1, 64, 17, 48], [3, 200, 27]):
+            s.reset()
+            pos = 0
+            for c in chunks:
+                lg = s.forward(ids[pos:pos + c])[0]
+                pos += c
+                assert rel_err(lg, ref[pos - 1]) < tol, (precision, chunks, pos)
+    finally:
+        gpt.destroy()
