@@ -19,8 +19,8 @@
 // Every sum of partial results runs in a fixed order (no float atomics), so results are reproducible. Weights
 // arrive in shared memory by bulk asynchronous copies issued before the dependency wait, i.e. while the previous
 // kernel is still running; the attention kernel re-uses its q/k/v weight buffer for its slice of the output
-// projection, fetched while the attention itself runs. No copy is multicast; remote shared memory is only ever
-// written with plain st.shared::cluster stores between cluster barriers.
+// projection, fetched while the attention itself runs. Every copy has one destination CTA; remote shared memory
+// is only ever written with plain st.shared::cluster stores between cluster barriers.
 #pragma once
 #include "common.cuh"
 #include "matmul.cuh"
