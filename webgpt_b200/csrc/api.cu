@@ -79,6 +79,7 @@ struct wgpt_device {
   bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
   uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
+  size_t gemv_rows_max_bytes;  // 2-8 rows: largest staged input (rows x K x 4) the register-streaming GEMV takes
   unsigned int *d_work;  // two counters of gemv_loop_kernel (left zero by every launch)
   bool loop_gemv;     // products against matrices larger than L2 through gemv_loop_kernel (WGPT_LOOP_GEMV=0: off)
   bool fused_decode;  // single-sequence decode with two kernels per block (WGPT_FUSED_DECODE=0 turns it off)
@@ -217,6 +218,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->graphs = !(ev && ev[0] == '0');
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
+  ev = getenv("WGPT_GEMV_ROWS_MAX_BYTES");
+  dev->gemv_rows_max_bytes = ev ? (size_t)atol(ev) : ~size_t(0);
   ev = getenv("WGPT_FUSED_DECODE");
   dev->fused_decode = !(ev && ev[0] == '0');
   ev = getenv("WGPT_LOOP_GEMV");
@@ -592,12 +595,13 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // Tensor map of a row-major FP32 matrix [rows, cols] with row stride ld (floats), boxes of 32 x 128 elements,
 // 128-byte swizzle, zero fill outside the matrix.
-static int32_t make_tile_map(CUtensorMap *map, const float *base, uint64_t rows, uint64_t cols, uint64_t ld) {
+static int32_t make_tile_map(CUtensorMap *map, const float *base, uint64_t rows, uint64_t cols, uint64_t ld,
+                             int box_rows = TC_BM) {
   EncodeTiledFn fn = encode_tiled_fn();
   REQUIRE(fn != nullptr, WGPT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * 4};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -660,6 +664,9 @@ static int32_t launch_gemm_tc(wgpt_device *dev, bool x3, const float *A, size_t 
   // Without split-K (a very wide product such as the de-embedding of up to 64 sequences) the exchanged form
   // finishes the values itself; it carries no activation or cache scatter.
   const bool exchanged = M <= 64 && (split_out != nullptr || (epi.act == 0 && epi.kc == nullptr));
+  // The exchanged form issues its instruction only as wide as the activation rows need (a multiple of 16) and
+  // fetches only those rows of the activation tile.
+  if (exchanged) TRY(make_tile_map(&ma, A, (uint64_t)M, (uint64_t)K, lda, M + 15 < TC_BN ? (M + 15) & ~15 : TC_BN));
   const int tw = exchanged ? TC_BM : N;
   const int n_work = tiles * splits;
   dim3 grid(n_work < dev->sm_count ? n_work : dev->sm_count);
@@ -1811,7 +1818,15 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     // a: [M,K] contiguous. Small M: weight-streaming GEMV with the LayerNorm fused in; otherwise a LayerNorm pass
     // into s->h (separate, or riding on the previous product's second stage) and a tiled GEMM. next_gamma/beta:
     // the LayerNorm that will consume this product's output rows e.out[M,N].
-    if (gemv_nk_fits(dev, M, K)) return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
+    if (gemv_nk_fits(dev, M, K)) {
+      // Several rows of a long K leave the register-streaming kernel one CTA of eight warps per SM (the rows
+      // fill shared memory): unless the shared-memory block form takes the product, the tiled GEMM is faster.
+      int bc = 0, bw = 0;
+      size_t bs = 0;
+      const bool block_form = dev->block_gemv && gemv_block_plan(dev, M, K, N, gamma != nullptr, &bc, &bw, &bs);
+      if (M == 1 || block_form || (size_t)M * K * 4 <= dev->gemv_rows_max_bytes)
+        return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
+    }
     const float *src = a;
     if (gamma) {
       if (!h_ready) TRY(launch_layernorm(dev, a, (size_t)K, gamma, beta, s->h, (size_t)K, M, K));

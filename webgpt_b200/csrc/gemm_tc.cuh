@@ -169,6 +169,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // tile is not split and the a_hi x b_lo product is not issued (two MMAs per k-step instead of three).
   const bool lo_tma = X3 && b_lo_tma == 1;
   const bool b_exact = X3 && b_lo_tma == 2;
+  // Exchanged operands: the second operand's live rows are the few activation rows, so the instruction is issued
+  // only as wide as they need (a multiple of 16 columns) and only that part of the tile is split into hi and lo.
+  const int n_mma = transposed ? min(TC_BN, (N + 15) & ~15) : TC_BN;
+  const uint32_t idesc = (TC_IDESC & ~(0x3Fu << 17)) | ((uint32_t)(n_mma >> 3) << 17);
+  // ... and the tensor map of that operand has a box of n_mma rows: bytes one stage receives
+  const uint32_t stage_tx = (uint32_t)TC_TILE_BYTES + (uint32_t)n_mma * (TC_BK * 4) + (lo_tma ? (uint32_t)TC_TILE_BYTES : 0u);
 #ifdef WGPT_TRACE
   __shared__ unsigned int tc_trace_base;  // the roles below are different threads: they share thread 0's record
   {
@@ -212,7 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pre = t.num_kb < S ? t.num_kb : S;
     for (int kb = 0; kb < pre; kb++) {
       uint8_t *st = tiles + (size_t)kb * Plan::kStageBytes;
-      mbar_expect_tx(&full[kb], (lo_tma ? 3 : 2) * TC_TILE_BYTES);
+      mbar_expect_tx(&full[kb], stage_tx);
       if (static_op == 1) {
         tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[kb]);
         if (lo_tma) tma_load_2d(st + 3 * TC_TILE_BYTES, &map_b_lo, (t.kb0 + kb) * TC_BK, t.n0, &full[kb]);
@@ -240,7 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             continue;
           }
           if (*abort_flag || !mbar_wait(&empty[s], (it & 1) ^ 1, TC_POLLS)) { *abort_flag = 1; break; }
-          mbar_expect_tx(&full[s], (lo_tma ? 3 : 2) * TC_TILE_BYTES);
+          mbar_expect_tx(&full[s], stage_tx);
           tma_load_2d(st, &map_a, (t.kb0 + kb) * TC_BK, t.m0, &full[s]);
           tma_load_2d(st + TC_TILE_BYTES, &map_b, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
           if (lo_tma) tma_load_2d(st + 3 * TC_TILE_BYTES, &map_b_lo, (t.kb0 + kb) * TC_BK, t.n0, &full[s]);
@@ -270,12 +276,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < TC_BK / 8; k++) {
             const uint64_t da = umma_desc_sw128(a_hi + k * 32), db = umma_desc_sw128(b_hi + k * 32);
-            umma_tf32(tmem_acc, da, db, TC_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_tf32(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             if (X3) {
               const uint64_t dal = umma_desc_sw128(a_hi + 2 * TC_TILE_BYTES + k * 32);
               const uint64_t dbl = umma_desc_sw128(b_hi + 2 * TC_TILE_BYTES + k * 32);
-              if (!b_exact) umma_tf32(tmem_acc, da, dbl, TC_IDESC, 1u);
-              umma_tf32(tmem_acc, dal, db, TC_IDESC, 1u);
+              if (!b_exact) umma_tf32(tmem_acc, da, dbl, idesc, 1u);
+              umma_tf32(tmem_acc, dal, db, idesc, 1u);
             }
           }
           umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
@@ -399,6 +405,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------- hi/lo split (warps 6-9) ----------------
     const int tix = threadIdx.x - 6 * 32;  // 0..127
     int kc = 0;
+    // 2 KiB pieces (16 tile rows) to split: the whole first tile, and of the second tile nothing when its low part
+    // came by TMA or is zero, otherwise the rows the instruction reads.
+    constexpr int kTilePieces = TC_TILE_BYTES / (16 * 128);
+    const int q_end = kTilePieces + ((lo_tma || b_exact) ? 0 : n_mma / 16);
     for (int w = blockIdx.x; w < n_work && !*abort_flag; w += gridDim.x) {
       const TcWork t = tc_work(w, m_tiles, n_tiles, kb_per_split, total_kb);
       for (int kb = 0; kb < t.num_kb; kb++, kc++) {
@@ -408,8 +418,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t hi = smem_addr(tiles + (size_t)s * Plan::kStageBytes) + (uint32_t)tix * 16u;
         const uint32_t lo = hi + 2 * TC_TILE_BYTES;
 #pragma unroll 8
-        for (int q = 0; q < (2 * TC_TILE_BYTES) / (16 * 128); q++) {
-          if ((lo_tma || b_exact) && q == TC_TILE_BYTES / (16 * 128)) break;  // the B tile's low part came by TMA, or is zero
+        for (int q = 0; q < q_end; q++) {
           // kind::tf32 reads the top 19 bits of each FP32 operand and ignores the rest (checked on B200: clearing
           // the low 13 bits first gives bit-identical products), so the staged tile itself serves as `hi`.
           float4 x = lds128(hi + (uint32_t)q * 2048u), l;
