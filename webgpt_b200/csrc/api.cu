@@ -79,7 +79,7 @@ struct wgpt_device {
   bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
   uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
-  size_t gemv_rows_max_bytes;  // 2-8 rows: largest staged input (rows x K x 4) the register-streaming GEMV takes
+  int gemv_stream_max_rows;  // most rows the register-streaming GEMV takes for a layer product (WGPT_GEMV_MAX_ROWS)
   unsigned int *d_work;  // two counters of gemv_loop_kernel (left zero by every launch)
   bool loop_gemv;     // products against matrices larger than L2 through gemv_loop_kernel (WGPT_LOOP_GEMV=0: off)
   bool fused_decode;  // single-sequence decode with two kernels per block (WGPT_FUSED_DECODE=0 turns it off)
@@ -218,8 +218,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->graphs = !(ev && ev[0] == '0');
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
-  ev = getenv("WGPT_GEMV_ROWS_MAX_BYTES");
-  dev->gemv_rows_max_bytes = ev ? (size_t)atol(ev) : ~size_t(0);
+  ev = getenv("WGPT_GEMV_MAX_ROWS");
+  dev->gemv_stream_max_rows = ev ? atoi(ev) : 5;
   ev = getenv("WGPT_FUSED_DECODE");
   dev->fused_decode = !(ev && ev[0] == '0');
   ev = getenv("WGPT_LOOP_GEMV");
@@ -1819,12 +1819,13 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     // into s->h (separate, or riding on the previous product's second stage) and a tiled GEMM. next_gamma/beta:
     // the LayerNorm that will consume this product's output rows e.out[M,N].
     if (gemv_nk_fits(dev, M, K)) {
-      // Several rows of a long K leave the register-streaming kernel one CTA of eight warps per SM (the rows
-      // fill shared memory): unless the shared-memory block form takes the product, the tiled GEMM is faster.
+      // Many rows of a long K leave the register-streaming kernel few warps per SM (the rows fill shared memory):
+      // unless the shared-memory block form takes the product, the tiled GEMM in its exchanged form is faster from
+      // six rows on (GPT-2 XL decode pass: 5.89 against 6.60 ms at eight rows, 5.50 against 5.16 ms at four).
       int bc = 0, bw = 0;
       size_t bs = 0;
       const bool block_form = dev->block_gemv && gemv_block_plan(dev, M, K, N, gamma != nullptr, &bc, &bw, &bs);
-      if (M == 1 || block_form || (size_t)M * K * 4 <= dev->gemv_rows_max_bytes)
+      if (block_form || M <= dev->gemv_stream_max_rows)
         return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
     }
     const float *src = a;
