@@ -1610,7 +1610,8 @@ struct wgpt_session {
   int cap_tok;   // tokens per forward the activation buffers are sized for
   int out_cap;   // capacity (per sequence) of d_out_ids
   int last_rows; // rows of the most recent forward (for the tap)
-  int n_split;
+  int n_split;        // position slices of the decode attention (attn_split_for), fixed while a step graph lives
+  bool split_forced;  // set by WGPT_ATTN_SPLIT
   float *x, *h, *q, *o, *f, *logits;
   float *kc, *vc;  // [n_layer][n_seq][n_ctx][E]
   float *fx_a = nullptr, *fx_b = nullptr;     // fused decode: residual stream entering the attention / MLP kernel
@@ -1657,6 +1658,21 @@ static int32_t session_reserve(wgpt_session *s, int n_tok) {
   return WGPT_OK;
 }
 
+// Position slices per (sequence, head) of the decode attention: 1, 2, 4 or 8 CTAs share a head's cache rows.
+// Doubled while the grid stays within a CTA budget: about two CTAs per SM for up to eight sequences with a short
+// context (the projection that follows merges the slices of every row in every CTA, so slices are not free
+// there), about five per SM for more sequences or a long context, where the attention itself is what costs.
+// Measured per decode pass, chosen / other: GPT-2 117M 16 rows 0.606 (4) / 0.645 (1), 32 rows 0.683 (2) / 0.711 (1),
+// 64 rows 0.791 (1) / 0.820 (2), 8 rows 0.574 (2) / 0.584 (8); GPT-2 XL at 768+ positions 8 sequences 6.57 (4) /
+// 7.46 (1), 16 sequences 6.70 (2) / 7.66 (1), 32 sequences 8.23 (1) / 8.28 (4) ms.
+constexpr int kMaxAttnSplit = 8;
+static int attn_split_for(const wgpt_device *dev, int n_head, int n_seq, int context_len) {
+  const int budget = (n_seq > 8 || context_len >= 512) ? (11 * dev->sm_count) / 2 : 2 * dev->sm_count;
+  int split = 1;
+  while (split < kMaxAttnSplit && n_head * n_seq * split * 2 <= budget) split *= 2;
+  return split;
+}
+
 WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_session **out) {
   REQUIRE(m && out, WGPT_ERR_ARG, "null argument");
   *out = nullptr;
@@ -1669,18 +1685,19 @@ WGPT_EXPORT int32_t wgpt_session_create(wgpt_model *m, int32_t n_seq, wgpt_sessi
   s->n_seq = n_seq;
   const wgpt_params &p = m->p;
   size_t kv = (size_t)p.n_layer * n_seq * p.n_ctx * p.n_embd;
-  // position slices per (sequence, head): a cluster of 1, 2, 4 or 8 CTAs, enough to put about two CTAs on every SM
-  int split = 1;
-  while (split < 8 && p.n_head * n_seq * split * 2 <= 2 * m->dev->sm_count) split *= 2;
+  s->split_forced = false;
   if (const char *ev = getenv("WGPT_ATTN_SPLIT")) {  // tuning override: 1, 2, 4 or 8
     int v = atoi(ev);
-    if (v == 1 || v == 2 || v == 4 || v == 8) split = v;
+    if (v == 1 || v == 2 || v == 4 || v == 8) {
+      s->n_split = v;
+      s->split_forced = true;
+    }
   }
-  s->n_split = split;
+  if (!s->split_forced) s->n_split = attn_split_for(m->dev, p.n_head, n_seq, 0);
   cudaError_t e = cudaMalloc(&s->kc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->vc, kv * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->logits, (size_t)n_seq * p.vocab_size * 4);
-  if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * s->n_split * (m->hs + 4) * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&s->attn_part, (size_t)n_seq * p.n_head * kMaxAttnSplit * (m->hs + 4) * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->attn_cnt, ((size_t)n_seq * p.n_head + 1) * 4);  // + arg-max done counter
   if (e == cudaSuccess) e = cudaMalloc(&s->next_ids, (size_t)n_seq * 4);
   if (e == cudaSuccess) e = cudaMalloc(&s->pick_val, (size_t)n_seq * p.vocab_size * 4);
@@ -2013,6 +2030,9 @@ static int32_t pick_and_advance(wgpt_session *s, int n_tok) {
 // step-dependent values are read from device memory, so one captured step serves every position.
 static int32_t decode_step(wgpt_session *s) {
   wgpt_device *dev = s->m->dev;
+  // the slice count follows the context length as it is when the step is (re)captured
+  if (!s->split_forced && (!dev->graphs || s->step_graph == nullptr))
+    s->n_split = attn_split_for(dev, s->m->p.n_head, s->n_seq, s->len);
   if (!dev->graphs) {
     return forward(s, s->next_ids, 1, true);
   }
