@@ -79,6 +79,7 @@ struct wgpt_device {
   bool capturing;   // between wgpt_graph_begin and wgpt_graph_end
   uint64_t capture_launch0;
   bool block_gemv;  // layer GEMVs through gemv_block_kernel (WGPT_BLOCK_GEMV=0: register-streaming kernel)
+  int deembed_tc_min_rows;   // fewest sequences whose de-embedding runs on the tensor-core GEMM (WGPT_DEEMBED_TC_ROWS)
   int gemv_stream_max_rows;  // most rows the register-streaming GEMV takes for a layer product (WGPT_GEMV_MAX_ROWS)
   unsigned int *d_work;  // two counters of gemv_loop_kernel (left zero by every launch)
   bool loop_gemv;     // products against matrices larger than L2 through gemv_loop_kernel (WGPT_LOOP_GEMV=0: off)
@@ -218,6 +219,8 @@ WGPT_EXPORT int32_t wgpt_device_create(int32_t ordinal, wgpt_device **out) {
   dev->graphs = !(ev && ev[0] == '0');
   ev = getenv("WGPT_BLOCK_GEMV");
   dev->block_gemv = !(ev && ev[0] == '0');
+  ev = getenv("WGPT_DEEMBED_TC_ROWS");
+  dev->deembed_tc_min_rows = ev ? atoi(ev) : 6;
   ev = getenv("WGPT_GEMV_MAX_ROWS");
   dev->gemv_stream_max_rows = ev ? atoi(ev) : 5;
   ev = getenv("WGPT_FUSED_DECODE");
@@ -1838,11 +1841,12 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
     if (gemv_nk_fits(dev, M, K)) {
       // Many rows of a long K leave the register-streaming kernel few warps per SM (the rows fill shared memory):
       // unless the shared-memory block form takes the product, the tiled GEMM in its exchanged form is faster from
-      // six rows on (GPT-2 XL decode pass: 5.89 against 6.60 ms at eight rows, 5.50 against 5.16 ms at four).
+      // six rows on (GPT-2 XL decode pass: 5.89 against 6.60 ms at eight rows, 5.50 against 5.16 ms at four). FP32
+      // mode keeps the GEMV: its GEMM runs on the CUDA cores.
       int bc = 0, bw = 0;
       size_t bs = 0;
       const bool block_form = dev->block_gemv && gemv_block_plan(dev, M, K, N, gamma != nullptr, &bc, &bw, &bs);
-      if (block_form || M <= dev->gemv_stream_max_rows)
+      if (block_form || M <= dev->gemv_stream_max_rows || dev->precision == WGPT_PRECISION_FP32)
         return launch_gemv_nk(dev, M, a, (size_t)K, gamma, beta, Wt, K, N, e);
     }
     const float *src = a;
@@ -1921,7 +1925,12 @@ static int32_t forward(wgpt_session *s, const uint32_t *ids, int n_tok, bool pic
   size_t ld_last = (size_t)n_tok * E;
   Epilogue e = plain_epi(s->logits, p.vocab_size, nullptr);
   s->last_rows = M;
-  if (gemv_nk_fits(dev, s->n_seq, E)) {
+  // Six or more sequences: the de-embedding streams faster through the tensor-core GEMM's exchanged form plus the
+  // arg-max kernel than through the looping GEMV with its fused pick (decode pass of GPT-2 117M 0.548 against
+  // 0.573 ms at eight rows, 0.503 / 0.518 at six, 0.427 / 0.419 at four). Not in FP32 mode, whose GEMM runs on
+  // the CUDA cores.
+  const bool deembed_tc = dev->precision != WGPT_PRECISION_FP32 && s->n_seq >= dev->deembed_tc_min_rows;
+  if (gemv_nk_fits(dev, s->n_seq, E) && !deembed_tc) {
     GreedyPick gp = no_pick();
     if (pick && s->sample_k == 0) {  // arg-max and position advance ride on the de-embedding kernel
       gp.pval = s->pick_val; gp.pidx = s->pick_idx; gp.counter = s->attn_cnt + (size_t)s->n_seq * H;
