@@ -678,7 +678,7 @@ gemv_block_kernel(const float *__restrict__ x, size_t ldx, const float *__restri
     // K chunk for all of the CTA's columns, eight columns at a time. A weight float4 is then read once per warp
     // (the eight row lanes share the address) and an input float4 once per column pass; with the K-in-lanes form
     // used for one row every warp re-read all M rows for every three columns (245 KB of shared-memory reads per
-    // CTA for an eight-row QKV product, 4 us, and 128 registers, which kept the next kernel off the SM).
+    // CTA for an eight-row QKV product, 4 us).
     constexpr int CB = 8;
     const int mrow = lane & 7, ksl = lane >> 3;
     const int mm = mrow < M ? mrow : M - 1;
